@@ -14,6 +14,8 @@ from . import vopedra as _vopedra  # registers the architecture
 from .vopedra import VopedraConfig
 from . import gozolix as _gozolix  # registers the architecture
 from .gozolix import GozolixConfig
+from . import lilupel as _lilupel  # registers the architecture
+from .lilupel import LilupelConfig
 
 
 def read_config_json(folder: str) -> dict:

@@ -27,6 +27,8 @@ class NormSpec:
     dim: int
     eps: float
     bias: bool = True
+    # the stored weight is the distance from this value (1.0: a weight stored around zero, applied as 1 + w)
+    weight_offset: float = 0.0
 
 
 @dataclass(frozen=True)

@@ -12,7 +12,8 @@
 //
 // A score may be shaped before the softmax: s = (q . k) * score_scale; with softcap > 0,
 // s <- softcap * tanh(s / softcap); with a slope per query head, s <- s - slope_h * (p - j) for the
-// key at position j (a penalty that grows with the distance).
+// key at position j (a penalty that grows with the distance).  A head may have a sink: a learned score that
+// joins the denominator of its softmax once, unscaled, with no key and no value.
 #include "common.cuh"
 
 struct MixedAttnArgs {
@@ -35,7 +36,18 @@ struct MixedAttnArgs {
     float score_scale;        // multiplies q . k
     float softcap;            // > 0: scores are capped smoothly at +-softcap
     const float* slopes;      // [nH] or null: head h's penalty per position of distance
+    const float* sinks;       // [nH] or null: e^(sinks[h]) joins the softmax's denominator of head h (no key, no value)
 };
+
+// What a sink does to a finished softmax with maximum m and sum l (of e^(s - m)): the factor on the weighted
+// values' sum, 1 / (l + e^(sink - m)), taken against the larger of m and the sink so that nothing overflows.
+__device__ __forceinline__ float am_finish(float m, float l, const float* sinks, int h) {
+    if (!sinks) return l > 0.f ? 1.0f / l : 0.f;
+    const float sink = sinks[h];
+    const float top = fmaxf(m, sink);
+    const float scale = m > -INFINITY ? expf(m - top) : 0.f;
+    return scale / (l * scale + expf(sink - top));
+}
 
 // the shaped score of query head h at position p and the key at position j
 __device__ __forceinline__ float am_shape(float dot, const MixedAttnArgs& a, float slope, int p, int j) {
@@ -133,7 +145,7 @@ attn_pairs_kernel(MixedAttnArgs a) {
         }
     }
     if (!live) return;
-    const float inv = l > 0.f ? 1.0f / l : 0.f;
+    const float inv = am_finish(m, l, a.sinks, g);
     float* o = a.pairs + (((size_t)(a.seq_qstart[b] + idx) * a.nH + g) * nVal + (a.mix ? vh : 0)) * vd;
 #pragma unroll
     for (int i = 0; i < NACC; ++i) {
@@ -226,7 +238,7 @@ attn_pairs_decode_kernel(MixedAttnArgs a) {
         const float mw = part[w * (vd + 2) + vd];
         if (mw > -INFINITY) ll += part[w * (vd + 2) + vd + 1] * expf(mw - mm);
     }
-    const float inv = ll > 0.f ? 1.0f / ll : 0.f;
+    const float inv = am_finish(mm, ll, a.sinks, g);
     float* o = a.pairs + (((size_t)row * a.nH + g) * nVal + (a.mix ? vh : 0)) * vd;
     for (int d = threadIdx.x; d < vd; d += blockDim.x) {
         float s = 0.f;
@@ -408,7 +420,7 @@ head_mix_split_kernel(MixedAttnArgs a) {
             coef[gi * a.splits + s] = e;
             den = fmaf(ml[2 * s + 1], e, den);
         }
-        const float w = (a.mix ? a.mix[h * a.nH + g] : 1.0f) * (den > 0.f ? 1.0f / den : 0.f);
+        const float w = (a.mix ? a.mix[h * a.nH + g] : 1.0f) * am_finish(mm, den, a.sinks, g);
         for (int s = 0; s < a.splits; ++s) coef[gi * a.splits + s] *= w;
     }
     __syncthreads();

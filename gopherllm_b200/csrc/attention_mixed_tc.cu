@@ -45,6 +45,7 @@ struct PairsArgs {
     const float* slopes;      // [nH] or null: s <- s - slope_h * (query position - key position)
     void* out;                // [T, nH*vd] bf16 or null: without a mixing table (nVal 1) the result goes here, rounded,
                               // and no second kernel has to read the 32-bit pairs again
+    const float* sinks;       // [nH] or null: e^(sinks[h]) joins the softmax's denominator of head h
 };
 
 __device__ __forceinline__ unsigned ap_smem(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
@@ -272,8 +273,17 @@ attn_pairs_tc_kernel(PairsArgs a) {
         l_run[i] += __shfl_xor_sync(0xffffffffu, l_run[i], 1);
         l_run[i] += __shfl_xor_sync(0xffffffffu, l_run[i], 2);
     }
-    const float inv_lo = l_run[0] > 0.f ? 1.f / l_run[0] : 0.f;
-    const float inv_hi = l_run[1] > 0.f ? 1.f / l_run[1] : 0.f;
+    float inv_lo = l_run[0] > 0.f ? 1.f / l_run[0] : 0.f;
+    float inv_hi = l_run[1] > 0.f ? 1.f / l_run[1] : 0.f;
+    if (a.sinks) {
+        // the sink joins the denominator once, against the larger of the row's maximum and itself
+        const float sink = a.sinks[h];
+        const float top_lo = fmaxf(m_run[0], sink), top_hi = fmaxf(m_run[1], sink);
+        const float sc_lo = m_run[0] > -INFINITY ? expf(m_run[0] - top_lo) : 0.f;
+        const float sc_hi = m_run[1] > -INFINITY ? expf(m_run[1] - top_hi) : 0.f;
+        inv_lo = sc_lo / (l_run[0] * sc_lo + expf(sink - top_lo));
+        inv_hi = sc_hi / (l_run[1] * sc_hi + expf(sink - top_hi));
+    }
     const int slot = a.nVal > 1 ? vh : 0;
     if (a.out && a.nVal == 1) {
         __nv_bfloat16* O = (__nv_bfloat16*)a.out;

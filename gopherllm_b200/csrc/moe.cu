@@ -746,3 +746,27 @@ GL_API int gl_moe_combine(const float* y, const float* add, float* out, int T, i
     return gl_launch(moe_combine_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, stream, 1, y, add, out, n, N, top) == 0
                ? GL_OK : GL_ERR_LAUNCH;
 }
+
+// ---------------------------------------------------------------------------
+// Routing without a router: a table [vocab, top] names every token id's experts, each with weight 1 / top.
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(256)
+moe_route_table_kernel(const int* tokens, const int* __restrict__ table, int* ids, float* weights, int n, int top, int vocab, int E) {
+    gl_grid_launch_dependents();
+    gl_grid_wait();
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const int t = i / top, k = i - t * top;
+    const int tok = gl_checked(tokens[t], vocab, GL_BAD_TOKEN);
+    ids[i] = gl_checked(table[(size_t)tok * top + k], E, GL_BAD_ROW);
+    weights[i] = 1.0f / (float)top;
+}
+
+GL_API int gl_moe_route_table(const int* tokens, const int* table, int* ids, float* weights, int T, int top, int vocab, int E,
+                              cudaStream_t stream) {
+    if (T <= 0) return GL_OK;
+    if (top <= 0 || vocab <= 0 || E <= 0) return GL_ERR_SHAPE;
+    const int n = T * top;
+    return gl_launch(moe_route_table_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, stream, 1, tokens, table, ids,
+                     weights, n, top, vocab, E);
+}

@@ -235,7 +235,8 @@ GL_API int gl_qkv_cache(const QkvCacheArgs* args, int act_dtype, int cache_dtype
 //   first 2*half dims of every head; q * q_scale to q_out; k and v into the token's cache row.
 // A query temperature that grows with the position may scale q as well:
 //   q * (1 + temp_coef * ln(floor((pos + 1) / temp_every) + 1))        (temp_every > 0)
-// and a mixer that reads the keys and values another one wrote brings queries alone (q_only).
+// and a mixer that reads the keys and values another one wrote brings queries alone (q_only).  With head_unit
+// every head of q and k is brought to unit root mean square after the rotation (no weight).
 // One block per token; statistics, rotation and scale in 32-bit.
 // ---------------------------------------------------------------------------
 struct QkvRowNormArgs {
@@ -255,6 +256,8 @@ struct QkvRowNormArgs {
     int n_pages;
     float temp_coef, temp_every;   // query temperature (temp_every <= 0: none)
     int q_only;                    // the rows hold queries alone; nothing is written to the cache
+    int head_unit;                 // after the rotation every head of q and k is divided by its own root mean square
+                                   // over hd (eps inside the root, no weight)
 };
 
 template <typename TA, typename TC>
@@ -310,6 +313,17 @@ qkv_rownorm_cache_kernel(QkvRowNormArgs a) {
             const float u = hv[i0], x = hv[i1];
             hv[i0] = u * c - x * s;
             hv[i1] = x * c + u * s;
+        }
+        __syncthreads();
+    }
+    if (a.head_unit) {
+        const int heads = a.nH + (a.q_only ? 0 : a.nKV);
+        for (int head = w; head < heads; head += (int)(blockDim.x >> 5)) {        // a warp a head
+            float* hv = v + (size_t)head * a.hd;
+            float q2 = 0.f;
+            for (int d = lane; d < a.hd; d += 32) q2 = fmaf(hv[d], hv[d], q2);
+            const float inv = 1.0f / sqrtf(gl_warp_sum(q2) / (float)a.hd + a.eps);
+            for (int d = lane; d < a.hd; d += 32) hv[d] *= inv;
         }
         __syncthreads();
     }

@@ -55,6 +55,12 @@ __device__ __forceinline__ float rc_decay(float x) {
 //       q times q_scale; beta = sigmoid(b), g = e^(-e^(A_log) softplus(a + dt_bias)) per head, from a second
 //       tensor of projections (``gates``: b at column i_off + h, a at f_off + h);
 //       S <- g S;  u = beta (v - S^T k);  S' = S + k u^T;  o = S'^T q.
+//   kind 3, plain decay: S' = keep S + take k v^T;  o = S'^T q + skip_h v.  q and k (shared by H / KVH heads) may be
+//       rotated by the token's position first (the first 2 rot_half dims of a head, dim i paired with i + rot_half,
+//       cosines and sines [T, rot_half] of the step's tokens) and are then scaled by q_scale and k_scale.  The
+//       decay is fixed per head (keep = lower[h], take = 1: retention) or follows a step size from a second tensor
+//       of projections (``gates``, column f_off + h): dt = softplus(x + dt_bias[h]), keep = e^(-e^(A_log[h]) dt),
+//       take = dt (a state-space layer with a scalar decay per head, whose B, x, C are this memory's k, v, q).
 // State row: S [H, D, V], then for kind 0 n [H, D] and m [H].  Every block of a head's columns reads n and m
 // when it starts, and blocks of one head may run one after the other, so the new n and m go to a scratch
 // [B, H, D + 1] first and a second kernel moves them into the rows once all blocks are done.
@@ -77,6 +83,12 @@ struct MemoryScanArgs {
     const float* dt_bias;     // [H]
     int gates_ld, KVH;        // KVH: heads of q and k (each shared by H / KVH heads of v)
     int rows_per_thread;      // 0: chosen by the grid's size; else 32, 8, 4, 2 or 1 (for measurements)
+    // kind 3:
+    const float* cosv;        // [T, rot_half] or null: q and k are rotated by the token's position
+    const float* sinv;
+    int rot_half;
+    float k_scale;            // multiplies k after the rotation
+    const float* d_skip;      // [H] or null: o += d_skip[h] * v
 };
 
 // FULL: D == R * DPT and D a multiple of 4, so a thread's rows are DPT / 4 groups of four consecutive ones read
@@ -101,7 +113,7 @@ memory_scan_kernel(MemoryScanArgs a, int R, int CH) {
     float* gs = vs + CH * CT;                   // [CHUNK][4]   kind 0: gi, gf, then keep, take; [.][3] reused
     float* es = gs + CH * 4;                    // [CHUNK]      kind 0: e^(-m')
 
-    const int kh = KIND == 2 ? h / (H / a.KVH) : h;   // the head of q and k this head reads
+    const int kh = (KIND == 2 || KIND == 3) ? h / (H / a.KVH) : h;   // the head of q and k this head reads
     float* srow = a.state + (size_t)a.seq_slot[b] * a.state_stride;
     float* S_g = srow + (size_t)h * D * V;
     const float* n_g = srow + (size_t)H * D * V + (size_t)h * D;
@@ -193,6 +205,20 @@ memory_scan_kernel(MemoryScanArgs a, int R, int CH) {
             } else if (KIND == 2) {
                 qs[e] = qp;
                 ks[e] = gl_load(row + a.k_off + kh * D + d);
+            } else if (KIND == 3) {
+                float qv = qp, kv = gl_load(row + a.k_off + kh * D + d);
+                if (a.cosv && d < 2 * a.rot_half) {
+                    // the pair (u, v) = (dim i, dim i + rot_half) becomes (u c - v s, v c + u s)
+                    const bool first = d < a.rot_half;
+                    const int i = first ? d : d - a.rot_half, other = first ? d + a.rot_half : d - a.rot_half;
+                    const float c = a.cosv[(size_t)(qstart + s0 + s) * a.rot_half + i];
+                    const float sn = a.sinv[(size_t)(qstart + s0 + s) * a.rot_half + i];
+                    const float qo = gl_load(row + a.q_off + kh * D + other), ko = gl_load(row + a.k_off + kh * D + other);
+                    qv = first ? qv * c - qo * sn : qv * c + qo * sn;
+                    kv = first ? kv * c - ko * sn : kv * c + ko * sn;
+                }
+                qs[e] = qv * a.q_scale;
+                ks[e] = kv * a.k_scale;
             } else {
                 qs[e] = rc_silu(qp);
                 const float l = a.lower[h * D + d];
@@ -225,6 +251,16 @@ memory_scan_kernel(MemoryScanArgs a, int R, int CH) {
                 }
             }
             if (fast && s0 + CH < qlen) fetch(s0 + CH);       // the next chunk's inputs travel while this one is walked
+        }
+        if (KIND == 3 && threadIdx.x < ns) {
+            float take = 1.0f, keep = a.lower ? a.lower[h] : 1.0f;
+            if (a.gates) {
+                const TA* row = (const TA*)a.gates + (size_t)(qstart + s0 + threadIdx.x) * a.gates_ld;
+                take = rc_softplus(gl_load(row + a.f_off + h) + a.dt_bias[h]);
+                keep = rc_decay(-expf(a.a_log[h]) * take);
+            }
+            gs[threadIdx.x * 4 + 0] = take;
+            gs[threadIdx.x * 4 + 1] = keep;
         }
         if (KIND == 0) {
             if (threadIdx.x < ns) {
@@ -320,6 +356,14 @@ memory_scan_kernel(MemoryScanArgs a, int R, int CH) {
                     part[i % PARTS] = fmaf(S[i], qr[i], part[i % PARTS]);
                 }
                 pending = PARTS == 4 ? (part[0] + part[1]) + (part[2] + part[3]) : part[0];
+            } else if (KIND == 3) {
+                const float keep = gs[s * 4 + 1];
+                const float tv = gs[s * 4 + 0] * v;
+#pragma unroll
+                for (int i = 0; i < DPT; ++i) {
+                    S[i] = fmaf(keep, S[i], kr[i] * tv);
+                    num = fmaf(S[i], qr[i], num);
+                }
             } else {
 #pragma unroll
                 for (int i = 0; i < DPT; ++i) {
@@ -341,6 +385,7 @@ memory_scan_kernel(MemoryScanArgs a, int R, int CH) {
             if (r == 0 && live) {
                 float o = num;
                 if (KIND == 0) o = num / (fmaxf(fabsf(nq), es[s]) + 1e-6f);
+                if (KIND == 3 && a.d_skip) o = fmaf(a.d_skip[h], v, o);
                 out_col[(size_t)(s0 + s) * H * V] = o;
             }
             }
@@ -400,6 +445,10 @@ static int launch_memory_scan(const MemoryScanArgs& a, cudaStream_t stream) {
         if (full) return gl_launch_in_order(memory_scan_kernel<TA, DPT, 2, true>, grid, dim3(MS_THREADS), smem, stream, a, R, CH);
         return gl_launch_in_order(memory_scan_kernel<TA, DPT, 2, false>, grid, dim3(MS_THREADS), smem, stream, a, R, CH);
     }
+    if (a.kind == 3) {
+        if (full) return gl_launch_in_order(memory_scan_kernel<TA, DPT, 3, true>, grid, dim3(MS_THREADS), smem, stream, a, R, CH);
+        return gl_launch_in_order(memory_scan_kernel<TA, DPT, 3, false>, grid, dim3(MS_THREADS), smem, stream, a, R, CH);
+    }
     if (full) return gl_launch_in_order(memory_scan_kernel<TA, DPT, 1, true>, grid, dim3(MS_THREADS), smem, stream, a, R, CH);
     return gl_launch_in_order(memory_scan_kernel<TA, DPT, 1, false>, grid, dim3(MS_THREADS), smem, stream, a, R, CH);
 }
@@ -454,8 +503,13 @@ GL_API int gl_memory_scan(const MemoryScanArgs* args, int act_dtype, cudaStream_
     const MemoryScanArgs& a = *args;
     if (a.B <= 0) return GL_OK;
     if (a.H <= 0 || a.D <= 0 || a.V <= 0 || a.D > 512 || a.B > 65535 || a.H > 65535) return GL_ERR_SHAPE;
-    if (a.kind < 0 || a.kind > 2) return GL_ERR_SHAPE;
+    if (a.kind < 0 || a.kind > 3) return GL_ERR_SHAPE;
     if (a.kind == 2 && (!a.gates || !a.a_log || !a.dt_bias || a.KVH <= 0 || a.H % a.KVH)) return GL_ERR_SHAPE;
+    if (a.kind == 3) {
+        if (a.KVH <= 0 || a.H % a.KVH) return GL_ERR_SHAPE;
+        if (a.gates ? (!a.a_log || !a.dt_bias) : !a.lower) return GL_ERR_SHAPE;
+        if (a.cosv && (!a.sinv || a.rot_half <= 0 || 2 * a.rot_half > a.D)) return GL_ERR_SHAPE;
+    }
     if (a.kind == 0 && (!(a.cap > 0.f) || !a.nm_next)) return GL_ERR_SHAPE;
     if (a.state_stride < (long long)a.H * a.D * a.V + (a.kind == 0 ? (long long)a.H * (a.D + 1) : 0)) return GL_ERR_SHAPE;
     if (act_dtype == GL_F32) return dispatch_memory_scan<float>(a, stream);
@@ -466,14 +520,16 @@ GL_API int gl_memory_scan(const MemoryScanArgs* args, int act_dtype, cudaStream_
 // ---------------------------------------------------------------------------
 // Per-head unit norm of a memory's output, a weight and an optional gate:
 //   out[t, h, j] = o[t, h, j] / sqrt(mean_j o[t, h, :]^2 + eps) * w * sigmoid(gate[t, h*V + j])
-// w is [H*V] (w_per_head = 1) or [V] shared by the heads; gate (activation type, row pitch
+// w is [H*V] (w_per_head = 1) or [V] shared by the heads (null: no weight); gate (activation type, row pitch
 // gate_ld, first column gate_off) may be absent; gate_silu multiplies by silu(gate) instead of the sigmoid.
+// gate_first: the gate comes before the norm, out = g / sqrt(mean_j g^2 + eps) * w with g = o * act(gate).
 // One warp per (token, head).
 // ---------------------------------------------------------------------------
 template <typename TA>
 __global__ void __launch_bounds__(128)
 head_norm_gate_kernel(const float* o, const float* __restrict__ w, const TA* gate, TA* __restrict__ out,
-                      long long items, int H, int V, int w_per_head, int gate_ld, int gate_off, float eps, int gate_silu) {
+                      long long items, int H, int V, int w_per_head, int gate_ld, int gate_off, float eps, int gate_silu,
+                      int gate_first) {
     gl_grid_launch_dependents();
     gl_grid_wait();
     const int lane = threadIdx.x & 31;
@@ -482,13 +538,22 @@ head_norm_gate_kernel(const float* o, const float* __restrict__ w, const TA* gat
     const long long t = item / H;
     const int h = (int)(item - t * H);
     const float* src = o + (size_t)item * V;
+    const TA* grow = gate ? gate + (size_t)t * gate_ld + gate_off + h * V : nullptr;
+    const bool early = gate && gate_first;
     float q = 0.f;
-    for (int j = lane; j < V; j += 32) { const float v = src[j]; q += v * v; }
+    for (int j = lane; j < V; j += 32) {
+        float v = src[j];
+        if (early) { const float z = gl_load(grow + j); v *= gate_silu ? rc_silu(z) : rc_sigmoid(z); }
+        q += v * v;
+    }
     const float inv = 1.0f / sqrtf(gl_warp_sum(q) / (float)V + eps);
     for (int j = lane; j < V; j += 32) {
-        float y = src[j] * inv * w[w_per_head ? h * V + j : j];
-        if (gate) {
-            const float z = gl_load(gate + (size_t)t * gate_ld + gate_off + h * V + j);
+        float y = src[j];
+        if (early) { const float z = gl_load(grow + j); y *= gate_silu ? rc_silu(z) : rc_sigmoid(z); }
+        y *= inv;
+        if (w) y *= w[w_per_head ? h * V + j : j];
+        if (gate && !early) {
+            const float z = gl_load(grow + j);
             y *= gate_silu ? rc_silu(z) : rc_sigmoid(z);
         }
         gl_store(out + (size_t)item * V + j, y);
@@ -497,17 +562,17 @@ head_norm_gate_kernel(const float* o, const float* __restrict__ w, const TA* gat
 
 GL_API int gl_head_norm_gate(const float* o, const float* w, const void* gate, void* out, int T, int H, int V,
                              int w_per_head, int gate_ld, int gate_off, float eps, int act_dtype, int gate_silu,
-                             cudaStream_t stream) {
+                             int gate_first, cudaStream_t stream) {
     if (T <= 0) return GL_OK;
     if (H <= 0 || V <= 0) return GL_ERR_SHAPE;
     const long long items = (long long)T * H;
     const dim3 grid((unsigned)((items + 3) / 4));
     if (act_dtype == GL_F32)
         return gl_launch(head_norm_gate_kernel<float>, grid, dim3(128), 0, stream, 1, o, w, (const float*)gate, (float*)out,
-                         items, H, V, w_per_head, gate_ld, gate_off, eps, gate_silu);
+                         items, H, V, w_per_head, gate_ld, gate_off, eps, gate_silu, gate_first);
     if (act_dtype == GL_BF16)
         return gl_launch(head_norm_gate_kernel<__nv_bfloat16>, grid, dim3(128), 0, stream, 1, o, w, (const __nv_bfloat16*)gate,
-                         (__nv_bfloat16*)out, items, H, V, w_per_head, gate_ld, gate_off, eps, gate_silu);
+                         (__nv_bfloat16*)out, items, H, V, w_per_head, gate_ld, gate_off, eps, gate_silu, gate_first);
     return GL_ERR_DTYPE;
 }
 

@@ -563,3 +563,94 @@ GL_API int gl_rms_norm_pair(const float* x, const float* g1, const float* g2, vo
     if (out_dtype == GL_BF16) return gl_launch(rms_norm_pair_kernel<__nv_bfloat16, 0>, dim3((unsigned)R), dim3(threads), 0, stream, 1, x, g1, g2, (__nv_bfloat16*)out1, (__nv_bfloat16*)out2, R, D, eps);
     return GL_ERR_DTYPE;
 }
+
+// ---------------------------------------------------------------------------
+// The 32-bit residual stream rounded to the activation type, for sublayers that read the stream itself
+// (a layer that norms what a sublayer returns, not what it reads).
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(256)
+round_rows_kernel(const float* x, __nv_bfloat16* __restrict__ out, long long n2) {
+    gl_grid_launch_dependents();
+    gl_grid_wait();
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n2; i += (long long)gridDim.x * blockDim.x) {
+        const float2 v = ((const float2*)x)[i];
+        ((__nv_bfloat162*)out)[i] = __floats2bfloat162_rn(v.x, v.y);
+    }
+}
+
+GL_API int gl_round_rows(const float* x, void* out, long long n, cudaStream_t stream) {
+    if (n <= 0) return GL_OK;
+    if (n % 2 || (((uintptr_t)x) & 7) || (((uintptr_t)out) & 3)) return GL_ERR_ALIGN;
+    const long long want = (n / 2 + 255) / 256;
+    return gl_launch(round_rows_kernel, dim3((unsigned)(want > 8192 ? 8192 : want)), dim3(256), 0, stream, 1, x,
+                     (__nv_bfloat16*)out, n / 2);
+}
+
+// ---------------------------------------------------------------------------
+// A sublayer's output normed and added onto the stream it was computed from:
+//   y = sa * a [+ sb * b];   out[t, :] = add[t, :] + y / sqrt(mean(y^2) + eps) * w
+// (32-bit rows; b may be absent: two branches of a sublayer are summed with their scales before the norm;
+// out may be add).  ``rounded``, if given, also receives out in bfloat16: the next sublayer's input.
+// One block per row; the row stays in shared memory between the two passes.
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(256)
+post_norm_add_kernel(const float* a, const float* b, const float* __restrict__ w, const float* add, float* out,
+                     __nv_bfloat16* rounded, int D, float eps, float sa, float sb) {
+    extern __shared__ float row[];
+    __shared__ float red[8];
+    gl_grid_launch_dependents();
+    gl_grid_wait();
+    const size_t base = (size_t)blockIdx.x * D;
+    float q = 0.f;
+    for (int d = threadIdx.x; d < D; d += blockDim.x) {
+        float y = sa * a[base + d];
+        if (b) y = fmaf(sb, b[base + d], y);
+        row[d] = y;
+        q = fmaf(y, y, q);
+    }
+    q = gl_warp_sum(q);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = q;
+    __syncthreads();
+    float tot = 0.f;
+    for (int i = 0; i < (int)(blockDim.x >> 5); ++i) tot += red[i];          // same order in every thread
+    const float inv = 1.0f / sqrtf(tot / (float)D + eps);
+    for (int d = threadIdx.x; d < D; d += blockDim.x) {
+        const float y = add[base + d] + row[d] * inv * w[d];
+        out[base + d] = y;
+        if (rounded) rounded[base + d] = __float2bfloat16_rn(y);
+    }
+}
+
+GL_API int gl_post_norm_add(const float* a, const float* b, const float* w, const float* add, float* out, void* rounded,
+                            int R, int D, float eps, float sa, float sb, cudaStream_t stream) {
+    if (R <= 0) return GL_OK;
+    if (D <= 0 || !a || !w || !add || !out) return GL_ERR_SHAPE;
+    const size_t smem = (size_t)D * sizeof(float);
+    if (smem > 48 * 1024) return GL_ERR_SMEM;
+    const int threads = D >= 2048 ? 256 : (D >= 512 ? 128 : 64);
+    return gl_launch(post_norm_add_kernel, dim3((unsigned)R), dim3(threads), smem, stream, 1, a, b, w, add, out,
+                     (__nv_bfloat16*)rounded, D, eps, sa, sb);
+}
+
+// ---------------------------------------------------------------------------
+// out = sa * a + sb * b [+ add0] [+ add1], 32-bit: two branches summed with a factor each.
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(256)
+scaled_sum_kernel(const float* a, const float* b, const float* add0, const float* add1, float* out, long long n, float sa, float sb) {
+    gl_grid_launch_dependents();
+    gl_grid_wait();
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+        float y = fmaf(sb, b[i], sa * a[i]);
+        if (add0) y += add0[i];
+        if (add1) y += add1[i];
+        out[i] = y;
+    }
+}
+
+GL_API int gl_scaled_sum(const float* a, const float* b, const float* add0, const float* add1, float* out, long long n,
+                         float sa, float sb, cudaStream_t stream) {
+    if (n <= 0) return GL_OK;
+    const long long want = (n + 255) / 256;
+    return gl_launch(scaled_sum_kernel, dim3((unsigned)(want > 8192 ? 8192 : want)), dim3(256), 0, stream, 1, a, b, add0, add1,
+                     out, n, sa, sb);
+}

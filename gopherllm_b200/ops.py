@@ -987,10 +987,11 @@ class _MemoryScanArgs(Structure):
                 ("B", c_int), ("H", c_int), ("D", c_int), ("V", c_int), ("state_stride", c_int), ("kind", c_int),
                 ("cap", c_float), ("q_scale", c_float), ("nm_next", c_void_p),
                 ("gates", c_void_p), ("a_log", c_void_p), ("dt_bias", c_void_p), ("gates_ld", c_int), ("KVH", c_int),
-                ("rows_per_thread", c_int)]
+                ("rows_per_thread", c_int),
+                ("cosv", c_void_p), ("sinv", c_void_p), ("rot_half", c_int), ("k_scale", c_float), ("d_skip", c_void_p)]
 
 
-MEMORY_GATED, MEMORY_BOUNDED_FORGET, MEMORY_DELTA = 0, 1, 2
+MEMORY_GATED, MEMORY_BOUNDED_FORGET, MEMORY_DELTA, MEMORY_DECAY = 0, 1, 2, 3
 MEMORY_SCAN_ROWS_PER_THREAD = 0     # 0: the kernel chooses by the grid's size; 32, 8, 4, 2 or 1 forces it (measurements)
 
 
@@ -1020,13 +1021,44 @@ def memory_scan(kind: int, proj: torch.Tensor, state: torch.Tensor, ctx, H: int,
                 q_off: int, k_off: int, v_off: int, i_off: int, f_off: int,
                 lower: Optional[torch.Tensor] = None, cap: float = 0.0, q_scale: float = 1.0,
                 gates: Optional[torch.Tensor] = None, a_log: Optional[torch.Tensor] = None,
-                dt_bias: Optional[torch.Tensor] = None, kv_heads: int = 0) -> torch.Tensor:
+                dt_bias: Optional[torch.Tensor] = None, kv_heads: int = 0,
+                decay: Optional[torch.Tensor] = None, cos: Optional[torch.Tensor] = None,
+                sin: Optional[torch.Tensor] = None, k_scale: float = 1.0,
+                skip: Optional[torch.Tensor] = None) -> torch.Tensor:
     """A matrix memory's run over the step's tokens: float32 [T, H*V], each head's S^T q (divided by the
     gated kind's normaliser); ``state`` [slots, size] float32 is read at ctx.seq_slot and written back.
     ``proj`` [T, ld] holds the projections at the given column offsets.  MEMORY_DELTA (the gated delta rule):
     q and k have ``kv_heads`` heads, each read by H / kv_heads heads; ``gates`` [T, ld'] holds the projection
-    behind beta at column i_off + h and the one behind the decay at f_off + h; ``a_log`` and ``dt_bias`` [H]."""
+    behind beta at column i_off + h and the one behind the decay at f_off + h; ``a_log`` and ``dt_bias`` [H].
+    MEMORY_DECAY: S <- keep S + take k v^T, o = S^T q + skip[h] v, with q and k of ``kv_heads`` heads (0: one per
+    head), rotated first where ``cos`` and ``sin`` [T, half] are given (dim i of a head with dim i + half), then
+    times q_scale and k_scale.  Either ``decay`` [H] (keep = decay[h], take = 1) or ``gates`` with ``a_log`` and
+    ``dt_bias`` [H]: dt = softplus(gates[t, f_off + h] + dt_bias[h]), keep = exp(-exp(a_log[h]) dt), take = dt."""
     _need(proj, "proj")
+    rot_half = 0
+    if kind == MEMORY_DECAY:
+        kv_heads = kv_heads or H
+        if kv_heads <= 0 or H % kv_heads:
+            raise KernelError(f"memory_scan: {H} heads do not share {kv_heads} heads of q and k")
+        if (decay is None) == (gates is None):
+            raise KernelError("memory_scan: a plain decay is either fixed per head or follows a step size")
+        if decay is not None:
+            _need(decay, "decay", torch.float32, (H,))
+        else:
+            _need(gates, "gates", proj.dtype)
+            _need(a_log, "a_log", torch.float32, (H,))
+            _need(dt_bias, "dt_bias", torch.float32, (H,))
+            if gates.shape[0] != proj.shape[0] or f_off + H > gates.shape[1]:
+                raise KernelError("memory_scan: the step sizes' columns do not fit")
+        if cos is not None:
+            rot_half = cos.shape[-1]
+            _need(cos, "cos", torch.float32, (proj.shape[0], rot_half))
+            _need(sin, "sin", torch.float32, (proj.shape[0], rot_half))
+            if 2 * rot_half > D:
+                raise KernelError("memory_scan: more rotated dims than a head has")
+        if skip is not None:
+            _need(skip, "skip", torch.float32, (H,))
+        lower = decay
     if kind == MEMORY_DELTA:
         _need(gates, "gates", proj.dtype)
         _need(a_log, "a_log", torch.float32, (H,))
@@ -1040,7 +1072,7 @@ def memory_scan(kind: int, proj: torch.Tensor, state: torch.Tensor, ctx, H: int,
     if kind == MEMORY_BOUNDED_FORGET:
         _need(lower, "lower", torch.float32, (H * D,))
     out = empty((T, H * V), torch.float32, proj.device)
-    if (USE_MEMORY_CHUNKS and kind != MEMORY_DELTA and ctx.max_qlen >= SCAN_CHUNKED_FROM
+    if (USE_MEMORY_CHUNKS and kind in (MEMORY_GATED, MEMORY_BOUNDED_FORGET) and ctx.max_qlen >= SCAN_CHUNKED_FROM
             and D <= MEMORY_CHUNKS_MAX_ROWS):
         # a long run: chunks of tokens side by side, a lane a column (two walks and a carry between them)
         gated = kind == MEMORY_GATED
@@ -1064,33 +1096,40 @@ def memory_scan(kind: int, proj: torch.Tensor, state: torch.Tensor, ctx, H: int,
                         ctx.seq_slot.data_ptr(), ctx.seq_qstart.data_ptr(), ctx.seq_qlen.data_ptr(),
                         ld, q_off, k_off, v_off, i_off, f_off, ctx.n_seqs, H, D, V, state.shape[1], kind, cap, q_scale,
                         _addr(nm), _addr(gates), _addr(a_log), _addr(dt_bias),
-                        gates.shape[1] if gates is not None else 0, kv_heads, MEMORY_SCAN_ROWS_PER_THREAD)
+                        gates.shape[1] if gates is not None else 0, kv_heads, MEMORY_SCAN_ROWS_PER_THREAD,
+                        _addr(cos) if rot_half else None, _addr(sin) if rot_half else None, rot_half, k_scale, _addr(skip))
     fn = _lib("recurrent.cu").gl_memory_scan
     _check(_launch(fn, byref(a), c_int(dtype_code(proj.dtype)), _stream()), "memory_scan", 2 if kind == MEMORY_GATED else 1)
     return out
 
 
-def head_norm_gate(o: torch.Tensor, w: torch.Tensor, H: int, V: int, eps: float, out_dtype: torch.dtype,
-                   gate: Optional[torch.Tensor] = None, gate_off: int = 0, gate_act: str = "sigmoid") -> torch.Tensor:
+def head_norm_gate(o: torch.Tensor, w: Optional[torch.Tensor], H: int, V: int, eps: float, out_dtype: torch.dtype,
+                   gate: Optional[torch.Tensor] = None, gate_off: int = 0, gate_act: str = "sigmoid",
+                   gate_first: bool = False) -> torch.Tensor:
     """Each head of float32 ``o`` [T, H*V] divided by its root mean square, times ``w`` ([H*V], or [V]
-    shared by the heads), times sigmoid (``gate_act`` "silu": silu) of the gate's columns gate_off.. of
-    ``gate`` [T, ld] if given."""
+    shared by the heads; None: no weight), times sigmoid (``gate_act`` "silu": silu) of the gate's columns
+    gate_off.. of ``gate`` [T, ld] if given.  ``gate_first``: the gate multiplies o before the norm, and the
+    root mean square is the gated values'."""
     if gate_act not in ("sigmoid", "silu"):
         raise KernelError(f"head_norm_gate: gate activation {gate_act!r} unknown")
     _need(o, "o", torch.float32)
     T = o.shape[0]
     _need(o, "o", shape=(T, H * V))
-    _need(w, "w", torch.float32)
-    if w.numel() not in (V, H * V):
-        raise KernelError(f"head_norm_gate: weight of {w.numel()} elements fits neither {V} nor {H * V}")
+    if w is not None:
+        _need(w, "w", torch.float32)
+        if w.numel() not in (V, H * V):
+            raise KernelError(f"head_norm_gate: weight of {w.numel()} elements fits neither {V} nor {H * V}")
     if gate is not None:
         _need(gate, "gate", out_dtype)
+        if gate_off + H * V > gate.shape[1]:
+            raise KernelError("head_norm_gate: the gate's columns do not fit its rows")
     out = empty((T, H * V), out_dtype, o.device)
     fn = _lib("recurrent.cu").gl_head_norm_gate
     _check(_launch(fn, _ptr(o), _ptr(w), _ptr(gate), _ptr(out), c_int(T), c_int(H), c_int(V),
-                   c_int(0 if w.numel() == V else 1),
+                   c_int(0 if w is None or w.numel() == V else 1),
                    c_int(0 if gate is None else gate.shape[1]), c_int(gate_off), c_float(eps),
-                   c_int(dtype_code(out_dtype)), c_int(1 if gate_act == "silu" else 0), _stream()), "head_norm_gate")
+                   c_int(dtype_code(out_dtype)), c_int(1 if gate_act == "silu" else 0), c_int(1 if gate_first else 0),
+                   _stream()), "head_norm_gate")
     return out
 
 
@@ -1180,16 +1219,19 @@ class _QkvRowNormArgs(Structure):
                 ("T", c_int), ("ld", c_int), ("nH", c_int), ("nKV", c_int), ("hd", c_int), ("vd", c_int),
                 ("half", c_int), ("max_pages", c_int), ("interleaved", c_int), ("write_kv", c_int),
                 ("eps", c_float), ("q_scale", c_float), ("n_pages", c_int),
-                ("temp_coef", c_float), ("temp_every", c_float), ("q_only", c_int)]
+                ("temp_coef", c_float), ("temp_every", c_float), ("q_only", c_int), ("head_unit", c_int)]
 
 
 def qkv_rownorm_to_cache(qkv: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, ctx, pages: torch.Tensor,
                          num_heads: int, num_kv_heads: int, head_dim: int, value_dim: int, q_scale: float,
                          cos: Optional[torch.Tensor], sin: Optional[torch.Tensor], interleaved: bool,
                          q_gamma: Optional[torch.Tensor], k_gamma: Optional[torch.Tensor], eps: float,
-                         write_kv: bool = True, q_temp: Optional[tuple] = None, q_only: bool = False) -> torch.Tensor:
+                         write_kv: bool = True, q_temp: Optional[tuple] = None, q_only: bool = False,
+                         head_unit: bool = False) -> torch.Tensor:
     """Queries and keys normalised over the whole projection (root mean square, weights [nH*hd] and
     [nKV*hd]; None: no norm), rotated and scaled; keys and values written to the tokens' cache rows.
+    ``head_unit``: after the rotation every head of q and k is divided by its own root mean square (eps
+    inside the root, no weight).
     qkv [T, ld]: q, k, v side by side from column 0 (``q_only``: queries alone, nothing is written).
     ``q_temp`` = (coef, every): q also times 1 + coef * ln(floor((position + 1) / every) + 1).
     Returns q [T, nH*hd]."""
@@ -1221,7 +1263,7 @@ def qkv_rownorm_to_cache(qkv: torch.Tensor, k_cache: torch.Tensor, v_cache: torc
                         T, ld, num_heads, num_kv_heads, head_dim, value_dim, half, pages.shape[-1],
                         1 if interleaved else 0, 1 if write_kv else 0, eps, q_scale, k_cache.shape[0],
                         q_temp[0] if q_temp is not None else 0.0, q_temp[1] if q_temp is not None else 0.0,
-                        1 if q_only else 0)
+                        1 if q_only else 0, 1 if head_unit else 0)
     fn = _lib("qkv_cache.cu").gl_qkv_rownorm_cache
     _check(_launch(fn, byref(a), c_int(dtype_code(qkv.dtype)), c_int(dtype_code(k_cache.dtype)), _stream()),
            "qkv_rownorm_to_cache")
@@ -1234,7 +1276,7 @@ class _MixedAttnArgs(Structure):
                 ("T", c_int), ("B", c_int), ("nH", c_int), ("nKV", c_int), ("hd", c_int), ("vd", c_int),
                 ("max_pages", c_int), ("window", c_int), ("max_qlen", c_int), ("n_pages", c_int),
                 ("parts", c_void_p), ("ml", c_void_p), ("splits", c_int), ("pages_per_split", c_int),
-                ("score_scale", c_float), ("softcap", c_float), ("slopes", c_void_p)]
+                ("score_scale", c_float), ("softcap", c_float), ("slopes", c_void_p), ("sinks", c_void_p)]
 
 
 # A block of the one-token kernel walks its pages one after the other and waits for each: what hides the trips to
@@ -1257,7 +1299,7 @@ class _PairsArgs(Structure):
                 ("seq_qstart", c_void_p), ("seq_qlen", c_void_p), ("seq_ctx", c_void_p), ("pages", c_void_p),
                 ("B", c_int), ("nH", c_int), ("nKV", c_int), ("nVal", c_int), ("max_pages", c_int), ("window", c_int),
                 ("max_qlen", c_int), ("score_scale", c_float), ("softcap", c_float), ("slopes", c_void_p),
-                ("out", c_void_p)]
+                ("out", c_void_p), ("sinks", c_void_p)]
 
 
 USE_PAIRS_TC = True
@@ -1266,11 +1308,13 @@ USE_PAIRS_TC = True
 def attention_mixed(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, ctx, pages: torch.Tensor,
                     num_heads: int, num_kv_heads: int, head_dim: int, value_dim: int,
                     mix: Optional[torch.Tensor] = None, window: int = 0, score_scale: float = 1.0,
-                    softcap: float = 0.0, slopes: Optional[torch.Tensor] = None) -> torch.Tensor:
+                    softcap: float = 0.0, slopes: Optional[torch.Tensor] = None,
+                    sinks: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Causal softmax attention of scaled queries [T, nH*hd] over the paged cache; with ``mix`` [nH, nH]
     head h applies sum_g mix[h, g] * (head g's softmax weights) to the values of its own key/value
     head.  A score is (q . k) * score_scale, then softcap * tanh(score / softcap) when softcap > 0, then
-    minus slopes[h] * (query position - key position) when ``slopes`` [nH] float32 is given.
+    minus slopes[h] * (query position - key position) when ``slopes`` [nH] float32 is given.  With ``sinks``
+    [nH] float32 the denominator of head h's softmax also holds exp(sinks[h]), once, with no key and no value.
     Returns [T, nH*vd] in q's type.  Prompts in bfloat16 with key and value sizes that are
     multiples of 16 compute the (query head, value head) pairs on the tensor cores (a library per pair
     of sizes); everything else runs the 32-bit kernels."""
@@ -1281,6 +1325,8 @@ def attention_mixed(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tenso
         _need(mix, "mix", torch.float32, (num_heads, num_heads))
     if slopes is not None:
         _need(slopes, "slopes", torch.float32, (num_heads,))
+    if sinks is not None:
+        _need(sinks, "sinks", torch.float32, (num_heads,))
     n_val = num_kv_heads if mix is not None else 1
     out = empty((T, num_heads * value_dim), q.dtype, q.device)
     pairs_tc = (USE_PAIRS_TC and ctx.max_qlen > 1 and q.dtype == torch.bfloat16 and k_cache.dtype == torch.bfloat16
@@ -1290,7 +1336,7 @@ def attention_mixed(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tenso
         p = _PairsArgs(q.data_ptr(), None, k_cache.data_ptr(), v_cache.data_ptr(),
                        ctx.seq_qstart.data_ptr(), ctx.seq_qlen.data_ptr(), ctx.seq_ctx.data_ptr(), pages.data_ptr(),
                        ctx.n_seqs, num_heads, num_kv_heads, 1, pages.shape[-1], window, ctx.max_qlen,
-                       score_scale, softcap, _addr(slopes), out.data_ptr())
+                       score_scale, softcap, _addr(slopes), out.data_ptr(), _addr(sinks))
         fn = _lib("attention_mixed_tc.cu", catalog.pair_dim_defines(head_dim, value_dim)).gl_attention_pairs_tc
         _check(_launch(fn, byref(p), _stream()), "attention_pairs_tc")
         return out
@@ -1298,7 +1344,7 @@ def attention_mixed(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tenso
     a = _MixedAttnArgs(q.data_ptr(), pairs.data_ptr(), out.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), _addr(mix),
                        ctx.seq_qstart.data_ptr(), ctx.seq_qlen.data_ptr(), ctx.seq_ctx.data_ptr(), pages.data_ptr(),
                        T, ctx.n_seqs, num_heads, num_kv_heads, head_dim, value_dim, pages.shape[-1], window,
-                       ctx.max_qlen, k_cache.shape[0], None, None, 0, 0, score_scale, softcap, _addr(slopes))
+                       ctx.max_qlen, k_cache.shape[0], None, None, 0, 0, score_scale, softcap, _addr(slopes), _addr(sinks))
     if ctx.max_qlen == 1 and num_heads // num_kv_heads <= 8 and num_kv_heads <= 8 and value_dim <= 128:
         # one token a sequence: the context in ranges of pages, a block each (sized for the step's longest
         # sequence; a captured step is sized for its bucket's longest), put together by the mixing kernel
@@ -1313,7 +1359,7 @@ def attention_mixed(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tenso
         p = _PairsArgs(q.data_ptr(), pairs.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(),
                        ctx.seq_qstart.data_ptr(), ctx.seq_qlen.data_ptr(), ctx.seq_ctx.data_ptr(), pages.data_ptr(),
                        ctx.n_seqs, num_heads, num_kv_heads, n_val, pages.shape[-1], window, ctx.max_qlen,
-                       score_scale, softcap, _addr(slopes), None)
+                       score_scale, softcap, _addr(slopes), None, _addr(sinks))
         fn = _lib("attention_mixed_tc.cu", catalog.pair_dim_defines(head_dim, value_dim)).gl_attention_pairs_tc
         _check(_launch(fn, byref(p), _stream()), "attention_pairs_tc")
         _check(_launch(lib.gl_head_mix, byref(a), c_int(dtype_code(q.dtype)), _stream()), "head_mix")
@@ -1513,6 +1559,75 @@ def rms_norm_pair(x: torch.Tensor, g1: torch.Tensor, g2: torch.Tensor, eps: floa
     _check(_launch(fn, _ptr(x), _ptr(g1), _ptr(g2), _ptr(o1), _ptr(o2), c_int(dtype_code(out_dtype)), c_int(R), c_int(D),
                    c_float(eps), _stream()), "rms_norm_pair")
     return o1, o2
+
+
+def round_rows(x: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
+    """The float32 residual stream in the activation type (itself when that is float32): the input of a
+    sublayer that reads the stream as it is."""
+    _need(x, "x", torch.float32)
+    if out_dtype == torch.float32:
+        return x
+    if out_dtype != torch.bfloat16:
+        raise KernelError(f"round_rows: {out_dtype} is not an activation type")
+    out = empty(x.shape, torch.bfloat16, x.device)
+    _check(_launch(_lib("rowwise.cu").gl_round_rows, _ptr(x), _ptr(out), ctypes.c_longlong(x.numel()), _stream()), "round_rows")
+    return out
+
+
+def post_norm_add(a: torch.Tensor, w: torch.Tensor, eps: float, add: torch.Tensor, out: Optional[torch.Tensor] = None,
+                  scale: float = 1.0, second=None, rounded: Optional[torch.dtype] = None):
+    """out = add + y / sqrt(mean(y^2) + eps) * w with y = scale * a (+ scale2 * a2 for ``second`` = (a2, scale2)),
+    float32 rows: a sublayer's output, or the weighted sum of its two branches, normed and added onto the
+    stream.  ``rounded`` = bfloat16 also returns the result rounded to that type (the next sublayer's input);
+    returns (out, rounded copy or None)."""
+    _need(a, "a", torch.float32)
+    R, D = a.shape
+    _need(w, "w", torch.float32, (D,))
+    _need(add, "add", torch.float32, (R, D))
+    a2, s2 = (None, 0.0)
+    if second is not None:
+        a2, s2 = second
+        _need(a2, "a2", torch.float32, (R, D))
+    if out is None:
+        out = empty((R, D), torch.float32, a.device)
+    _need(out, "out", torch.float32, (R, D))
+    copy = empty((R, D), torch.bfloat16, a.device) if rounded == torch.bfloat16 else None
+    fn = _lib("rowwise.cu").gl_post_norm_add
+    _check(_launch(fn, _ptr(a), _ptr(a2), _ptr(w), _ptr(add), _ptr(out), _ptr(copy), c_int(R), c_int(D), c_float(eps),
+                   c_float(scale), c_float(s2), _stream()), "post_norm_add")
+    return out, copy
+
+
+def scaled_sum(a: torch.Tensor, sa: float, b: torch.Tensor, sb: float, adds=(), out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """out = sa * a + sb * b + sum(adds), float32 tensors of one shape; up to two adds."""
+    _need(a, "a", torch.float32)
+    _need(b, "b", torch.float32, tuple(a.shape))
+    adds = list(adds)
+    if len(adds) > 2:
+        raise KernelError("scaled_sum adds at most two tensors")
+    for t in adds:
+        _need(t, "add", torch.float32, tuple(a.shape))
+    adds += [None] * (2 - len(adds))
+    if out is None:
+        out = empty(a.shape, torch.float32, a.device)
+    _need(out, "out", torch.float32, tuple(a.shape))
+    _check(_launch(_lib("rowwise.cu").gl_scaled_sum, _ptr(a), _ptr(b), _ptr(adds[0]), _ptr(adds[1]), _ptr(out),
+                   ctypes.c_longlong(a.numel()), c_float(sa), c_float(sb), _stream()), "scaled_sum")
+    return out
+
+
+def moe_route_table(tokens: torch.Tensor, table: torch.Tensor, experts: int):
+    """Routing by token id: (ids int32 [T, top], weights float32 [T, top]) with ids[t] = table[tokens[t]] and
+    every weight 1 / top."""
+    _need(tokens, "tokens", torch.int32)
+    _need(table, "table", torch.int32)
+    T = tokens.shape[0]
+    vocab, top = table.shape
+    ids = empty((T, top), torch.int32, tokens.device)
+    weights = empty((T, top), torch.float32, tokens.device)
+    _check(_launch(_lib("moe.cu").gl_moe_route_table, _ptr(tokens), _ptr(table), _ptr(ids), _ptr(weights), c_int(T), c_int(top),
+                   c_int(vocab), c_int(experts), _stream()), "moe_route_table")
+    return ids, weights
 
 
 def rms_scale_add(a: torch.Tensor, w: torch.Tensor, eps: float, alpha: float, adds=(), out: Optional[torch.Tensor] = None,

@@ -149,7 +149,11 @@ class MixedHeadAttention(Mixer):
     the 32-bit score (``q_scale`` multiplies q before it is rounded).  ``softcap`` c > 0: score <- c tanh(score / c).
     ``distance_bias`` x > 0: head h's score loses slope_h * (i - j) for the key at position j <= i, slope_h =
     2^(-x (h + 1) / heads).  ``shared_kv``: the mixer has no key and value projections; it reads the cache
-    entry another mixer with the same head counts and sizes wrote."""
+    entry another mixer with the same head counts and sizes wrote.  ``qk_norm`` = "head_unit": after the
+    rotation every head of q and of k is divided by its own root mean square (``norm_eps`` inside the root, no
+    weight).  ``sink``: a learned score per head ("sink" [heads]) whose exponential joins the softmax's
+    denominator once, with no key and no value, unscaled.  ``out_bias``: the output projection has a bias.
+    ``spec.window`` w > 0: a query sees itself and the w - 1 positions before it."""
 
     deferred_add = True
     capturable = True
@@ -163,9 +167,13 @@ class MixedHeadAttention(Mixer):
         if spec.head_dim > 256 or self.vdim > 256:
             raise ValueError(f"head sizes {spec.head_dim}/{self.vdim} exceed what the attention kernels take (256)")
         scope = spec.option("qk_norm", None)
-        if scope not in (None, "projection"):
-            raise ValueError(f"qk_norm {scope!r}: this mixer norms over the whole projection or not at all")
+        if scope not in (None, "projection", "head_unit"):
+            raise ValueError(f"qk_norm {scope!r}: this mixer norms over the whole projection, every head to unit "
+                             f"root mean square after the rotation, or not at all")
         self.row_norm = scope == "projection"
+        self.head_unit = scope == "head_unit"
+        self.sink = bool(spec.option("sink", False))
+        self.out_bias = bool(spec.option("out_bias", False))
         self.talk = bool(spec.option("talk", False))
         self.eps = float(spec.option("norm_eps", 1e-6))
         self.position = build_position(spec.position)
@@ -180,9 +188,10 @@ class MixedHeadAttention(Mixer):
                 raise ValueError("q_temp: the period must be positive")
         if self.softcap < 0 or self.distance_bias < 0:
             raise ValueError("softcap and distance_bias must not be negative")
-        if self.shared_kv and self.row_norm:
+        if self.shared_kv and (self.row_norm or self.head_unit):
             raise ValueError("a mixer that reads another one's keys has no key norm of its own")
         self.w_qkv = self.b_qkv = self.w_out = self.q_gamma = self.k_gamma = self.mix = self.slopes = None
+        self.b_out = self.sinks = None
 
     def parameters(self) -> Dict[str, ParamSpec]:
         s = self.spec
@@ -200,6 +209,10 @@ class MixedHeadAttention(Mixer):
             p["k_norm.weight"] = ParamSpec((kv,), "vector", "gamma")
         if self.talk:
             p["talk"] = ParamSpec((s.num_heads, s.num_heads), "vector", "wide")
+        if self.sink:
+            p["sink"] = ParamSpec((s.num_heads,), "vector", "wide")
+        if self.out_bias:
+            p["o.bias"] = ParamSpec((s.hidden,), "vector", "bias")
         return p
 
     def load(self, t: Dict[str, torch.Tensor]) -> None:
@@ -224,13 +237,14 @@ class MixedHeadAttention(Mixer):
         self.w_out = t["o.weight"]
         self.q_gamma, self.k_gamma = t.get("q_norm.weight"), t.get("k_norm.weight")
         self.mix = t.get("talk")
+        self.sinks, self.b_out = t.get("sink"), t.get("o.bias")
 
     def cache_request(self):
         s = self.spec
         return KVRequest(s.num_kv_heads, s.head_dim, s.window, value_dim=0 if self.vdim == s.head_dim else self.vdim)
 
     def products(self):
-        return [("qkv", self.w_qkv, self.b_qkv, None), ("o", self.w_out, None, None)]
+        return [("qkv", self.w_qkv, self.b_qkv, None), ("o", self.w_out, self.b_out, None)]
 
     def first_product(self):
         return self.w_qkv, self.b_qkv, None
@@ -246,20 +260,20 @@ class MixedHeadAttention(Mixer):
         q = ops.qkv_rownorm_to_cache(qkv, cache.k, cache.v, ctx, pages, s.num_heads, s.num_kv_heads, s.head_dim,
                                      self.vdim, s.q_scale, cos, sin, s.position.interleaved,
                                      self.q_gamma, self.k_gamma, self.eps, write_kv=cache.writes,
-                                     q_temp=self.q_temp, q_only=self.shared_kv)
+                                     q_temp=self.q_temp, q_only=self.shared_kv, head_unit=self.head_unit)
         o = ops.attention_mixed(q, cache.k, cache.v, ctx, pages, s.num_heads, s.num_kv_heads, s.head_dim, self.vdim,
                                 mix=self.mix, window=s.window, score_scale=self.score_scale, softcap=self.softcap,
-                                slopes=self.slopes)
-        return o, self.w_out, None
+                                slopes=self.slopes, sinks=self.sinks)
+        return o, self.w_out, self.b_out
 
     def forward(self, xn, ctx, cache, add: Sequence[torch.Tensor], out=None) -> torch.Tensor:
         if len(add) > 2:
             raise ValueError("at most two tensors can be added in the projection's epilogue")
-        o, w, _ = self.until_last(xn, ctx, cache)
+        o, w, b = self.until_last(xn, ctx, cache)
         add = [a() if callable(a) else a for a in add]
         a0 = add[0] if len(add) > 0 else None
         a1 = add[1] if len(add) > 1 else None
-        return ops.linear(o, w, None, add0=a0, add1=a1, out_dtype=torch.float32, out=out)
+        return ops.linear(o, w, b, add0=a0, add1=a1, out_dtype=torch.float32, out=out)
 
 
 register_mixer("attention", Attention)

@@ -196,6 +196,41 @@ class TwoNormParallelBlock(AssembledBlock):
         return x
 
 
+class PostNormBlock(AssembledBlock):
+    """x <- x + norm(mixer(x)); x <- x + norm2(ffn(x)): the sublayers read the residual stream itself (rounded to
+    the activation type where that is not 32-bit) and what they return is RMS-normed before it is added.  A layer
+    without a feed-forward (``spec.ffn`` None, no norm2) is the first half alone.  A mixer that offers
+    ``branches`` (two outputs with a factor each) is summed in the pass that norms and adds; that pass also
+    leaves the stream's rounded copy for the feed-forward."""
+
+    def __init__(self, spec: BlockSpec):
+        if (spec.ffn is None) != (spec.norm2 is None):
+            raise ValueError("the second norm comes with the feed-forward: both or neither")
+        super().__init__(spec)
+        for n in (self.norm, self.norm2):
+            if n is not None and not (getattr(n, "rms", False) and n.fusable is not None and not n.spec.bias):
+                raise ValueError("a block that norms its sublayers' outputs takes RMS norms without bias")
+
+    def forward(self, x, ctx, cache):
+        h = ops.round_rows(x, ctx.act_dtype)
+        w, _, eps, _ = self.norm.fusable()
+        copy = ctx.act_dtype if self.ffn is not None and ctx.act_dtype != torch.float32 else None
+        branches = getattr(self.mixer, "branches", None)
+        if branches is not None:
+            (a, sa), (b, sb) = branches(h, ctx, cache)
+            _, h = ops.post_norm_add(a, w, eps, add=x, out=x, scale=sa, second=(b, sb), rounded=copy)
+        else:
+            y = self.mixer.forward(h, ctx, cache, (), None)
+            _, h = ops.post_norm_add(y, w, eps, add=x, out=x, rounded=copy)
+        if self.ffn is None:
+            return x
+        w2, _, eps2, _ = self.norm2.fusable()
+        y = self.ffn.forward(h if h is not None else x, ctx, (), None)
+        ops.post_norm_add(y, w2, eps2, add=x, out=x)
+        return x
+
+
 register_block("parallel", ParallelBlock)
 register_block("parallel_two_norms", TwoNormParallelBlock)
 register_block("sequential", SequentialBlock)
+register_block("post_norm", PostNormBlock)

@@ -115,8 +115,10 @@ class MixtureOfExperts(FeedForward):
     experts of the best ``keep`` groups can be chosen (one group: every expert can).  The chosen experts'
     outputs are summed with weights score / (sum of the chosen scores + 1e-20) * ``router_scale``.  A shared
     expert of the same form (``shared`` > 0: its inner size) runs for every token and is added.
-    Options: ``experts``, ``top``, ``groups``, ``keep``, ``router_scale``, ``shared``; ``intermediate`` is an
-    expert's inner size."""
+    With ``router`` = "table" there is no router: a table of integers [``vocab``, top] names every token id's
+    experts (the entries of a row differ), and each counts 1 / top.
+    Options: ``experts``, ``top``, ``groups``, ``keep``, ``router_scale``, ``shared``, ``router``, ``vocab``;
+    ``intermediate`` is an expert's inner size."""
     capturable = True
     launches_only = True
 
@@ -126,17 +128,26 @@ class MixtureOfExperts(FeedForward):
         self.groups, self.keep = int(spec.option("groups", 1)), int(spec.option("keep", 1))
         self.scale = float(spec.option("router_scale", 1.0))
         self.shared = int(spec.option("shared", 0))
+        self.router = str(spec.option("router", "scores"))
+        self.vocab = int(spec.option("vocab", 0))
+        if self.router not in ("scores", "table"):
+            raise ValueError(f"moe: router {self.router!r} is neither scores nor table")
+        if self.router == "table" and self.vocab < 1:
+            raise ValueError("moe: a table of experts by token id needs the vocabulary's size")
         if spec.activation != "silu":
             raise ValueError("the experts' activation is silu")
         if not (0 < self.top <= self.E and self.groups >= 1 and self.E % self.groups == 0
                 and 1 <= self.keep <= self.groups and self.keep * (self.E // self.groups) >= self.top):
             raise ValueError(f"moe: top {self.top} of {self.E} experts in {self.groups} groups of which "
                              f"{self.keep} stay is not possible")
-        self.w_router = self.w_router_16 = self.w_gu = self.w_down = self.ws_gu = self.ws_down = None
+        self.w_router = self.w_router_16 = self.w_gu = self.w_down = self.ws_gu = self.ws_down = self.table = None
 
     def parameters(self) -> Dict[str, ParamSpec]:
         s, F = self.spec, self.spec.intermediate
-        p = {"router.weight": ParamSpec((self.E, s.hidden), "vector", "wide")}
+        if self.router == "table":
+            p = {"table": ParamSpec((self.vocab, self.top), "table_int", f"distinct:{self.E}")}
+        else:
+            p = {"router.weight": ParamSpec((self.E, s.hidden), "vector", "wide")}
         for e in range(self.E):
             p[f"e{e}.gate.weight"] = ParamSpec((F, s.hidden))
             p[f"e{e}.up.weight"] = ParamSpec((F, s.hidden))
@@ -148,16 +159,21 @@ class MixtureOfExperts(FeedForward):
         return p
 
     def load(self, t: Dict[str, torch.Tensor]) -> None:
-        self.w_router = t["router.weight"]
-        # Router weights whose values bfloat16 holds exactly (a 16-bit checkpoint's are) may go through the
-        # tensor cores: the products are then exact and the sums 32-bit, which is what "32-bit logits" asks for.
-        as16 = self.w_router.to(torch.bfloat16)
-        self.w_router_16 = as16.contiguous() if bool((as16.float() == self.w_router).all()) else None
+        if self.router == "table":
+            self.table = t["table"]
+            if int(self.table.min()) < 0 or int(self.table.max()) >= self.E:
+                raise ValueError(f"moe: the table names experts outside 0..{self.E - 1}")
+        else:
+            self.w_router = t["router.weight"]
+            # Router weights whose values bfloat16 holds exactly (a 16-bit checkpoint's are) may go through the
+            # tensor cores: the products are then exact and the sums 32-bit, which is what "32-bit logits" asks for.
+            as16 = self.w_router.to(torch.bfloat16)
+            self.w_router_16 = as16.contiguous() if bool((as16.float() == self.w_router).all()) else None
         mats = [t[f"e{e}.{n}.weight"] for e in range(self.E) for n in ("gate", "up", "down")]
         if len({m.dtype for m in mats}) > 1:
             t = dict(t)
             for k in list(t):
-                if k != "router.weight":
+                if k not in ("router.weight", "table"):
                     t[k] = t[k].float()
         # every expert's gate rows, then its up rows: [E, 2F, hidden]; the down weights [E, hidden, F]
         self.w_gu = torch.stack([torch.cat([t[f"e{e}.gate.weight"], t[f"e{e}.up.weight"]], 0)
@@ -168,13 +184,15 @@ class MixtureOfExperts(FeedForward):
             self.ws_down = t["shared.down.weight"]
 
     def products(self):
-        out = [("router", self.w_router, None, None)]
+        out = [("router", self.w_router, None, None)] if self.router != "table" else []
         if self.shared:
             out += [("shared.gate_up", self.ws_gu, None, None), ("shared.down", self.ws_down, None, None)]
         return out
 
-    def route(self, xn):
+    def route(self, xn, ctx=None):
         """(experts int32 [T, top], weights float32 [T, top]) of the step's tokens."""
+        if self.router == "table":
+            return ops.moe_route_table(ctx.tokens, self.table, self.E)
         if xn.dtype == torch.bfloat16 and self.w_router_16 is not None and xn.shape[1] % 8 == 0:
             logits = ops.linear(xn, self.w_router_16, None, out_dtype=torch.float32)
             return ops.moe_route(logits, self.top, self.groups, self.keep, self.scale)
@@ -183,7 +201,7 @@ class MixtureOfExperts(FeedForward):
     def forward(self, xn, ctx, add: Sequence[torch.Tensor], out=None) -> torch.Tensor:
         if len(add) > (2 if self.shared else 1):
             raise ValueError("more tensors to add than this feed-forward's kernels take")
-        ids, weights = self.route(xn)
+        ids, weights = self.route(xn, ctx)
         out = ops.moe_experts(xn, ids, weights, self.w_gu, self.w_down, add=add[0] if len(add) > 0 else None, out=out)
         if self.shared:
             gu = ops.linear(xn, self.ws_gu, None, out_dtype=ctx.act_dtype)

@@ -23,13 +23,16 @@ class LayerNorm(Norm):
         self.bias: Optional[torch.Tensor] = None
 
     def parameters(self) -> Dict[str, ParamSpec]:
-        p = {"weight": ParamSpec((self.spec.dim,), "vector", "gamma")}
+        # (a weight stored as its distance from weight_offset is drawn around zero in the random-weights mode)
+        p = {"weight": ParamSpec((self.spec.dim,), "vector", "bias" if self.spec.weight_offset else "gamma")}
         if self.spec.bias:
             p["bias"] = ParamSpec((self.spec.dim,), "vector", "beta")
         return p
 
     def load(self, tensors: Dict[str, torch.Tensor]) -> None:
         self.weight = tensors["weight"]
+        if self.spec.weight_offset:
+            self.weight = (self.weight + float(self.spec.weight_offset)).contiguous()
         self.bias = tensors.get("bias")
 
     def fusable(self):

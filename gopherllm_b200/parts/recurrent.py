@@ -1,4 +1,4 @@
-"""Mixers that carry a fixed-size state per sequence instead of a growing cache, and a mixer made of two.
+"""Mixers that carry a fixed-size state per sequence instead of a growing cache, and mixers made of two.
 
 Each asks the cache for a row of 32-bit state per sequence (``StateRequest``), zero when a sequence
 starts; a step reads the row, walks the step's tokens of that sequence and writes it back, so whole
@@ -14,7 +14,7 @@ import torch
 
 from .. import ops
 from ..config.specs import MixerSpec
-from .base import Mixer, ParamSpec, StateRequest, build_mixer, register_mixer
+from .base import Mixer, ParamSpec, StateRequest, build_mixer, build_position, register_mixer
 
 
 def _pad8(n: int) -> int:
@@ -343,8 +343,198 @@ class NormedPair(Mixer):
                                  second=(yr, self.w_right))
 
 
+class Retention(Mixer):
+    """Linear attention with a fixed decay per head and neither softmax nor denominator.  q = W_q h, k = W_k h
+    (heads of ``head_dim``), v = W_v h (heads of ``value_dim``), no biases; q and k pass the mixer's position
+    encoding (rotation of the first dims of every head), k is then multiplied by head_dim^(-1/2);
+        S <- decay_h S + k v^T;  o = S^T q
+    per head, from a zero state.  Each head's o is divided by its root mean square (``norm_eps``, no weight), the
+    heads are joined, multiplied by silu(W_g h) and projected.  The rotation, the scale, the decay and the state
+    are 32-bit.  Options: ``decay`` (one factor per head), ``norm_eps``."""
+    capturable = True
+    launches_only = True
+    deferred_add = True
+
+    def __init__(self, spec: MixerSpec):
+        self.spec = spec
+        self.H, self.D, self.V = spec.num_heads, spec.head_dim, spec.value_dim or spec.head_dim
+        self.eps = float(spec.option("norm_eps", 1e-6))
+        decay = spec.option("decay")
+        if decay is None or len(decay) != self.H or not all(0.0 < float(d) <= 1.0 for d in decay):
+            raise ValueError(f"retention: one decay in (0, 1] for each of the {self.H} heads expected, got {decay!r}")
+        self.decay_values = tuple(float(d) for d in decay)
+        self.position = build_position(spec.position)
+        self.state_size = ops.memory_state_size(ops.MEMORY_DECAY, self.H, self.D, self.V)
+        self.w_in = self.w_o = self.decay = None
+
+    def parameters(self) -> Dict[str, ParamSpec]:
+        H, D, V, W = self.H, self.D, self.V, self.spec.hidden
+        return {"q.weight": ParamSpec((H * D, W)), "k.weight": ParamSpec((H * D, W)),
+                "v.weight": ParamSpec((H * V, W)), "g.weight": ParamSpec((H * V, W)),
+                "o.weight": ParamSpec((W, H * V))}
+
+    def load(self, t: Dict[str, torch.Tensor]) -> None:
+        names = ("q", "k", "v", "g")
+        self.w_in, _ = _joined([t[n + ".weight"] for n in names], [None] * len(names), t["q.weight"])
+        self.w_o = t["o.weight"]
+        self.decay = torch.tensor(self.decay_values, dtype=torch.float64).to(torch.float32).to(self.w_in.device)
+        H, D, V = self.H, self.D, self.V
+        self.off = dict(q=0, k=H * D, v=2 * H * D, g=2 * H * D + H * V)
+
+    def cache_request(self):
+        return StateRequest((self.state_size,))
+
+    def first_product(self):
+        return self.w_in, None, None
+
+    def products(self):
+        return [("in", self.w_in, None, None), ("o", self.w_o, None, None)]
+
+    def until_last(self, xn, ctx, cache, first=None):
+        proj = first if first is not None else ops.linear(xn, self.w_in, None, out_dtype=ctx.act_dtype)
+        o = self.off
+        tables = self.position.tables(ctx)
+        cos, sin = tables if tables is not None else (None, None)
+        mem = ops.memory_scan(ops.MEMORY_DECAY, proj, cache.rows, ctx, self.H, self.D, self.V,
+                              o["q"], o["k"], o["v"], 0, 0, q_scale=1.0, k_scale=float(self.D) ** -0.5,
+                              decay=self.decay, cos=cos, sin=sin)
+        y = ops.head_norm_gate(mem, None, self.H, self.V, self.eps, ctx.act_dtype, gate=proj, gate_off=o["g"],
+                               gate_act="silu")
+        return y, self.w_o, None
+
+    def forward(self, xn, ctx, cache, add: Sequence, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        y, w, _ = self.until_last(xn, ctx, cache)
+        return _finish(y, w, add, out)
+
+
+class StateSpaceDual(Mixer):
+    """Mamba-2: a state-space layer whose decay is one number per head and token, so that a head is a matrix
+    memory S [state, value_dim] with keys B, values x and queries C.  With inner = heads * value_dim and
+    ``groups`` groups of B and C (head h reads group h / (heads / groups)):
+        W_in h = [z: inner | x: inner | B: groups * state | C: groups * state | dt: heads];
+        x, B and C together pass a causal convolution per channel (``conv`` taps, bias, the last tap is the current
+        token's, zeros before the start) and silu;
+        dt = softplus(dt + dt_bias);  S <- exp(-exp(A_log_h) dt) S + dt B x^T;  y = S^T C + D_h x;
+        y silu(z) is RMS-normed in ``norm_groups`` equal parts, each by its own root mean square (``norm_eps``),
+        times a weight [inner], and projected.
+    The state row holds S [heads, state, value_dim] and the convolution's last taps - 1 inputs; step sizes,
+    decays and the state are 32-bit.  Options: ``state``, ``groups``, ``conv``, ``norm_groups``, ``norm_eps``."""
+    capturable = True
+    launches_only = True
+    deferred_add = True
+
+    def __init__(self, spec: MixerSpec):
+        self.spec = spec
+        self.H, self.P = spec.num_heads, spec.value_dim or spec.head_dim
+        self.N, self.G = int(spec.option("state")), int(spec.option("groups", 1))
+        self.taps, self.parts = int(spec.option("conv", 1)), int(spec.option("norm_groups", 1))
+        self.eps = float(spec.option("norm_eps", 1e-6))
+        self.inner = self.H * self.P
+        if self.G < 1 or self.H % self.G:
+            raise ValueError(f"mamba2: {self.H} heads do not form {self.G} equal groups")
+        if self.parts < 1 or self.inner % self.parts:
+            raise ValueError(f"mamba2: {self.inner} channels do not form {self.parts} equal parts for the norm")
+        if self.taps < 1:
+            raise ValueError("mamba2: the convolution has at least one tap")
+        self.C = self.inner + 2 * self.G * self.N                       # convolved channels: x, B, C
+        self.tail_off = ops.memory_state_size(ops.MEMORY_DECAY, self.H, self.N, self.P)
+        self.state_size = self.tail_off + self.C * (self.taps - 1)
+        self.w_in = self.conv_w = self.conv_b = self.dt_bias = self.a_log = self.d_skip = self.norm = self.w_o = None
+
+    def parameters(self) -> Dict[str, ParamSpec]:
+        W = self.spec.hidden
+        return {"in.weight": ParamSpec((2 * self.inner + 2 * self.G * self.N + self.H, W)),
+                "conv.weight": ParamSpec((self.C, self.taps), "vector", "wide"),
+                "conv.bias": ParamSpec((self.C,), "vector", "bias"),
+                "dt_bias": ParamSpec((self.H,), "vector", "wide"), "A_log": ParamSpec((self.H,), "vector", "bias"),
+                "D": ParamSpec((self.H,), "vector", "gamma"), "norm.weight": ParamSpec((self.inner,), "vector", "gamma"),
+                "o.weight": ParamSpec((W, self.inner))}
+
+    def load(self, t: Dict[str, torch.Tensor]) -> None:
+        self.w_in, _ = _joined([t["in.weight"]], [None], t["in.weight"])
+        self.conv_w, self.conv_b = t["conv.weight"], t["conv.bias"]
+        self.dt_bias, self.a_log, self.d_skip = t["dt_bias"], t["A_log"], t["D"]
+        self.norm, self.w_o = t["norm.weight"], t["o.weight"]
+
+    def cache_request(self):
+        return StateRequest((self.state_size,))
+
+    def first_product(self):
+        return self.w_in, None, None
+
+    def products(self):
+        return [("in", self.w_in, None, None), ("o", self.w_o, None, None)]
+
+    def until_last(self, xn, ctx, cache, first=None):
+        proj = first if first is not None else ops.linear(xn, self.w_in, None, out_dtype=ctx.act_dtype)
+        inner, GN = self.inner, self.G * self.N
+        xbc = ops.conv_silu(proj, self.conv_w, self.conv_b, cache.rows, self.tail_off, ctx, x_off=inner)
+        # keys B, values x, queries C; the step sizes are still in the projection
+        mem = ops.memory_scan(ops.MEMORY_DECAY, xbc, cache.rows, ctx, self.H, self.N, self.P,
+                              inner + GN, inner, 0, 0, 2 * inner + 2 * GN, gates=proj, a_log=self.a_log,
+                              dt_bias=self.dt_bias, kv_heads=self.G, skip=self.d_skip)
+        y = ops.head_norm_gate(mem, self.norm, self.parts, inner // self.parts, self.eps, ctx.act_dtype, gate=proj,
+                               gate_off=0, gate_act="silu", gate_first=True)
+        return y, self.w_o, None
+
+    def forward(self, xn, ctx, cache, add: Sequence, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        y, w, _ = self.until_last(xn, ctx, cache)
+        return _finish(y, w, add, out)
+
+
+class ScaledPair(Mixer):
+    """Two mixers side by side on the same input, summed with a factor each: left_scale * left(h) +
+    right_scale * right(h).  The children are whole mixer specs (options ``left`` and ``right``); their cache
+    needs travel together as a pair.  ``branches`` hands a block the two outputs and their factors unsummed, so
+    that it can sum them in the pass that norms the result.  Options: ``left``, ``right``, ``left_scale``,
+    ``right_scale``."""
+    deferred_add = True
+
+    def __init__(self, spec: MixerSpec):
+        self.spec = spec
+        self.left, self.right = build_mixer(spec.option("left")), build_mixer(spec.option("right"))
+        self.left_scale, self.right_scale = float(spec.option("left_scale", 1.0)), float(spec.option("right_scale", 1.0))
+
+    @property
+    def capturable(self):
+        return self.left.capturable and self.right.capturable
+
+    @property
+    def launches_only(self):
+        return self.left.launches_only and self.right.launches_only
+
+    def parameters(self) -> Dict[str, ParamSpec]:
+        p = {f"left.{k}": v for k, v in self.left.parameters().items()}
+        p.update({f"right.{k}": v for k, v in self.right.parameters().items()})
+        return p
+
+    def load(self, t: Dict[str, torch.Tensor]) -> None:
+        self.left.load({k[len("left."):]: v for k, v in t.items() if k.startswith("left.")})
+        self.right.load({k[len("right."):]: v for k, v in t.items() if k.startswith("right.")})
+
+    def cache_request(self):
+        return (self.left.cache_request(), self.right.cache_request())
+
+    def products(self):
+        return ([("left." + n, w, b, a) for n, w, b, a in self.left.products()]
+                + [("right." + n, w, b, a) for n, w, b, a in self.right.products()])
+
+    def branches(self, xn, ctx, cache):
+        """[(float32 output, factor)] of the two children."""
+        return [(self.left.forward(xn, ctx, cache[0], (), None), self.left_scale),
+                (self.right.forward(xn, ctx, cache[1], (), None), self.right_scale)]
+
+    def forward(self, xn, ctx, cache, add: Sequence, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        (yl, sl), (yr, sr) = self.branches(xn, ctx, cache)
+        add = [a() if callable(a) else a for a in add]
+        return ops.scaled_sum(yl, sl, yr, sr, adds=add, out=out)
+
+
 register_mixer("mlstm", MatrixLstm)
 register_mixer("hgrn2", GatedLinearMemory)
 register_mixer("mamba1", SelectiveScan)
 register_mixer("normed_pair", NormedPair)
 register_mixer("gated_delta", GatedDeltaRule)
+register_mixer("retention", Retention)
+register_mixer("mamba2", StateSpaceDual)
+register_mixer("scaled_pair", ScaledPair)

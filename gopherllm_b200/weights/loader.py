@@ -188,10 +188,15 @@ def _tensor_seed(seed: int, name: str) -> int:
 def random_tensor(name: str, spec: ParamSpec, seed: int, sigma: float, storage: torch.dtype) -> torch.Tensor:
     """One declared tensor of the random-weights mode, drawn on the CPU from a generator seeded by
     (seed, name), in float32, and rounded to ``storage``."""
-    if spec.kind == "table_int":
-        return torch.zeros(spec.shape, dtype=torch.int32)
     g = torch.Generator(device="cpu")
     g.manual_seed(_tensor_seed(seed, name))
+    if spec.kind == "table_int":
+        if spec.init.startswith("distinct:"):      # every row: different numbers below the bound, drawn at random
+            bound = int(spec.init.split(":")[1])
+            rows = int(torch.tensor(spec.shape[:-1]).prod()) if len(spec.shape) > 1 else 1
+            picks = torch.rand((rows, bound), generator=g).argsort(-1)[:, :spec.shape[-1]]
+            return picks.reshape(spec.shape).to(torch.int32)
+        return torch.zeros(spec.shape, dtype=torch.int32)
     z = torch.randn(spec.shape, generator=g, dtype=torch.float32)
     if spec.init == "normal":
         t = z.mul_(sigma)
