@@ -5,6 +5,7 @@
     python bench.py --model phi-1.5          the same measurements at Phi-1.5's layer sizes
     python bench.py --ragged                 64 unequal prompts as one batch through Model.generate
     python bench.py --design gozolix         the same for a Gozolix model, beside a Vopedra model of equal width and depth
+    python bench.py --design lilupel         the same for a Lilupel model, beside a Vopedra model of equal width and depth
     python bench.py --design vopedra         prefill and decode of a Vopedra model at a few layer sizes beside a
                                              Phi model of equal width, depth and feed-forward weights
 
@@ -118,7 +119,7 @@ def main():
     ap.add_argument("--sections", default="decode,e2e,prefill,points",
                     help="which measurements to run (for profiling a part): decode,e2e,prefill,points")
     ap.add_argument("--model", default="phi-2", choices=sorted(MODELS), help="whose layer sizes to run")
-    ap.add_argument("--design", default=None, choices=["vopedra", "gozolix"],
+    ap.add_argument("--design", default=None, choices=["vopedra", "gozolix", "lilupel"],
                     help="instead: prefill and decode rates of another design at a few layer sizes, beside the Phi "
                          "model of equal width and depth")
     ap.add_argument("--ragged", action="store_true",
@@ -148,8 +149,8 @@ def main():
 
     if args.design == "vopedra":
         return design_vopedra(args)
-    if args.design == "gozolix":
-        return design_vopedra(args, design="gozolix")
+    if args.design in ("gozolix", "lilupel"):
+        return design_vopedra(args, design=args.design)
     pk, pk_src = peaks()
     label, sizes, weight_seed = MODELS[args.model]
     cfg = dict(sizes)
@@ -358,10 +359,34 @@ def gozolix_sizes(width, heads, ff):
             "embedding": {"scale": 1.0, "bigram": {"buckets": 65521, "mul_prev": 31, "mul_cur": 7}}, "layers": five + second}
 
 
+def lilupel_sizes(width, heads, ff):
+    """A Lilupel model whose layers resemble a real model's at this width, ten layer runs: two state-space layers
+    (inner size twice the width in heads of 64, a state of 128), a windowed attention (512 positions) beside a
+    retention, a state-space layer, and the pair once more on the first pair's weights; twice.  Every layer has a
+    mixture of 32 experts by token id, 4 a token, that together hold as many weights as a dense feed-forward."""
+    hd = width // heads
+    ssd = {"heads": 2 * width // 64, "vdim": 64, "state": 128, "groups": 8, "conv": 4, "norm_groups": 8}
+    pair = {"left": {"heads": heads, "kv_heads": max(1, heads // 4), "dim": hd, "vdim": hd, "scale": hd ** -0.5,
+                     "mask": {"size": 512}, "rot": {"dims": hd, "base": 10000.0}},
+            "right": {"heads": max(1, heads // 2), "dim": hd, "vdim": 2 * hd,
+                      "decay": [1.0 - 2.0 ** (-5 - i % 4) for i in range(max(1, heads // 2))],
+                      "rot": {"dims": hd, "base": 1000000.0}},
+            "left_scale": 1.0, "right_scale": 1.0}
+    moe = {"kind": "moe", "expert": {"ff": max(64, ff // 4 // 64 * 64)}, "router": {"experts": 32, "top": 4}}
+    five = [{"type": "mamba2", "mixer": ssd, "mlp": moe}, {"type": "mamba2", "mixer": ssd, "mlp": moe},
+            {"type": "parallel", "mixer": pair, "mlp": moe}, {"type": "mamba2", "mixer": ssd, "mlp": moe},
+            {"type": "parallel", "mixer": pair, "mlp": moe, "weights_of": 2}]
+    second = json.loads(json.dumps(five))
+    second[4]["weights_of"] = 7
+    return {"architecture": "Lilupel", "vocab": 32000, "width": width, "norm": {"eps": 1e-6}, "initializer_range": 0.02,
+            "layers": five + second}
+
+
 def design_vopedra(args, design="vopedra"):
     """Prefill and decode rates of Vopedra models (random weights) beside Phi models of the same width, the
-    same number of layer runs and feed-forwards of the same number of weights; with ``design`` "gozolix", of
-    Gozolix models beside Vopedra models of the same width and number of layer runs.  One JSON line."""
+    same number of layer runs and feed-forwards of the same number of weights; with ``design`` "gozolix" or
+    "lilupel", of models of that design beside Vopedra models of the same width and number of layer runs.  One
+    JSON line."""
     import numpy as np
     import torch
     import gopherllm_b200 as gl
@@ -422,16 +447,17 @@ def design_vopedra(args, design="vopedra"):
     clocks.start()
     rows = []
     for width, heads, ff_gated, ff_plain in ((1024, 16, 2752, 4096), (2048, 32, 5504, 8192)):
-        if design == "gozolix":
-            rows.append({"width": width, "heads": heads, "gozolix": measure(gozolix_sizes(width, heads, ff_gated)),
+        if design in ("gozolix", "lilupel"):
+            sizes = gozolix_sizes if design == "gozolix" else lilupel_sizes
+            rows.append({"width": width, "heads": heads, design: measure(sizes(width, heads, ff_gated)),
                          "vopedra": measure(vopedra_sizes(width, heads, ff_gated))})
             continue
         v = measure(vopedra_sizes(width, heads, ff_gated))
         phi = dict(PHI15, hidden_size=width, num_attention_heads=heads, num_key_value_heads=heads,
                    intermediate_size=ff_plain, vocab_size=32000, num_hidden_layers=v["layer_runs"])
         rows.append({"width": width, "heads": heads, "vopedra": v, "phi": measure(phi)})
-    if design == "gozolix":
-        print(json.dumps({"metric": "prefill and decode rates of Gozolix layer sizes beside Vopedra of equal width and depth (bf16)",
+    if design in ("gozolix", "lilupel"):
+        print(json.dumps({"metric": f"prefill and decode rates of {design.capitalize()} layer sizes beside Vopedra of equal width and depth (bf16)",
                           "unit": "tokens/s", "n_gpus": 1, "dtype": "bf16", "data": "synthetic: random weights seed 7, uniform token ids",
                           "decode_steps_timed": K, "decode_context": 1024, "peaks": pk_src, "clocks": clocks.stop(), "sizes": rows}))
         return 0

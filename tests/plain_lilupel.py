@@ -29,8 +29,8 @@ def silu(z):
 
 def rotate(x, rot, first_position=0):
     """x [T, heads, dim]: the first rot.dims dims of every head turned by position * base^(-2i/dims), dim i
-    paired with dim i + dims/2; the other dims stay."""
-    n = int(rot["dims"])
+    paired with dim i + dims/2; the other dims stay.  No ``rot`` entry, or zero dims: nothing is turned."""
+    n = int(rot["dims"]) if rot else 0
     if n == 0:
         return x
     T = x.shape[0]
@@ -49,8 +49,8 @@ def window_attention(h, w, pre, m, eps):
     q = (h @ w[pre + "q"].T + w[pre + "q.b"]).view(T, H, D)
     k = (h @ w[pre + "k"].T + w[pre + "k.b"]).view(T, G, D)
     v = (h @ w[pre + "v"].T + w[pre + "v.b"]).view(T, G, V)
-    q = unit_rms(rotate(q, m["rot"]), eps)
-    k = unit_rms(rotate(k, m["rot"]), eps)
+    q = unit_rms(rotate(q, m.get("rot")), eps)
+    k = unit_rms(rotate(k, m.get("rot")), eps)
     pos = torch.arange(T)
     dist = pos[:, None] - pos[None, :]
     visible = (dist >= 0) & (dist < int(m["mask"]["size"]))
@@ -69,8 +69,8 @@ def retention(h, w, pre, m, eps):
     """Linear attention with a fixed decay per head: S <- decay S + k v^T, o = S^T q; no softmax."""
     T = h.shape[0]
     H, D, V = m["heads"], m["dim"], m["vdim"]
-    q = rotate((h @ w[pre + "q"].T).view(T, H, D), m["rot"])
-    k = rotate((h @ w[pre + "k"].T).view(T, H, D), m["rot"]) * D ** -0.5
+    q = rotate((h @ w[pre + "q"].T).view(T, H, D), m.get("rot"))
+    k = rotate((h @ w[pre + "k"].T).view(T, H, D), m.get("rot")) * D ** -0.5
     v = (h @ w[pre + "v"].T).view(T, H, V)
     out = torch.zeros(T, H, V, dtype=h.dtype)
     for head in range(H):
