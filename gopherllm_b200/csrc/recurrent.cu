@@ -893,6 +893,11 @@ GL_API int gl_selective_scan(const SelectiveScanArgs* args, int act_dtype, cudaS
 //           max(|n.q|, e^-m) + 1e-6 follows as a pass of its own over all tokens at once).
 // The gated kind's gates come from a pass of their own: the log gates of all tokens side by side, then the
 // running maximum token by token (a thread a head), which leaves keep, take and e^-m per token.
+// The plain decay (kind 3) is the gated kind without a normaliser: keep and take per (token, head) come from a pass
+// of their own (a fixed decay, or a step size: the formulas of memory_scan_kernel), a = keep for every row,
+// b = k after its rotation and scale, and the token's value is multiplied by take before it enters, so that a
+// chunk's arithmetic is the token-by-token kernel's.  q and k heads may be shared by several heads; the skip
+// term d_skip[h] v is added to the read-out.
 // ---------------------------------------------------------------------------
 struct MemoryChunkArgs {
     const void* proj;         // [T, ld] activation type
@@ -910,6 +915,15 @@ struct MemoryChunkArgs {
     int T, ld, q_off, k_off, v_off, i_off, f_off;
     int B, H, D, V, cols, state_stride, kind, chunk_len, n_chunks;
     float cap, q_scale;
+    // kind 3:
+    const void* gates_in;     // [T, gates_ld] activation type or null: the step sizes' projections (column f_off + h)
+    const float* a_log;       // [H]
+    const float* dt_bias;     // [H]
+    const float* cosv;        // [T, rot_half] or null
+    const float* sinv;
+    const float* d_skip;      // [H] or null
+    int gates_ld, KVH, rot_half;
+    float k_scale;
 };
 
 #define MC_THREADS 128
@@ -960,6 +974,24 @@ memory_gate_walk_kernel(MemoryChunkArgs a) {
     if (lane == 0) *m_g = m;
 }
 
+// the plain decay's keep and take of every token: gates[t, h, 0] = keep, gates[t, h, 1] = take
+template <typename TA>
+__global__ void __launch_bounds__(256)
+memory_decay_gates_kernel(MemoryChunkArgs a) {
+    gl_grid_launch_dependents();
+    gl_grid_wait();
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= (long long)a.T * a.H) return;
+    const int t = (int)(i / a.H), h = (int)(i - (long long)t * a.H);
+    float take = 1.0f, keep = a.lower ? a.lower[h] : 1.0f;
+    if (a.gates_in) {
+        take = rc_softplus(gl_load((const TA*)a.gates_in + (size_t)t * a.gates_ld + a.f_off + h) + a.dt_bias[h]);
+        keep = rc_decay(-expf(a.a_log[h]) * take);
+    }
+    a.gates[i * 4 + 0] = keep;
+    a.gates[i * 4 + 1] = take;
+}
+
 // the product of a chunk's decays per row
 template <typename TA, int KIND>
 __global__ void __launch_bounds__(128)
@@ -974,30 +1006,33 @@ memory_chunk_decay_kernel(MemoryChunkArgs a) {
     float p = 1.0f;
     const float l = KIND == 1 ? a.lower[h * a.D + d] : 0.f;
     for (int s = t0; s < t1; ++s) {
-        if (KIND == 0) p *= a.gates[((size_t)(qstart + s) * a.H + h) * 4];
+        if (KIND == 0 || KIND == 3) p *= a.gates[((size_t)(qstart + s) * a.H + h) * 4];
         else p *= l + (1.0f - l) * rc_sigmoid(gl_load((const TA*)a.proj + (size_t)(qstart + s) * a.ld + a.f_off + h * a.D + d));
     }
     a.chunk_decay[(((size_t)b * a.n_chunks + chunk) * a.H + h) * a.D + d] = p;
 }
 
-// MODE 1: from zero, keep the last state.  MODE 2: from the chunk's start, with outputs.
-template <typename TA, int DMAX, int KIND, int MODE>
-__global__ void __launch_bounds__(MC_THREADS)
+// MODE 1: from zero, keep the last state.  MODE 2: from the chunk's start, with outputs.  NT: threads (columns) a block.
+template <typename TA, int DMAX, int KIND, int MODE, int NT>
+__global__ void __launch_bounds__(NT)
 memory_chunk_walk_kernel(MemoryChunkArgs a) {
     extern __shared__ __align__(16) float smem[];
     gl_grid_wait();
     const int D = a.D, V = a.V, H = a.H, cols = a.cols;
     const int b = blockIdx.z / a.n_chunks, chunk = blockIdx.z - b * a.n_chunks, h = blockIdx.y;
-    const int col0 = blockIdx.x * MC_THREADS, col = col0 + threadIdx.x;
+    const int col0 = blockIdx.x * NT, col = col0 + threadIdx.x;
     const bool live = col < cols;
     const int qlen = a.seq_qlen[b], qstart = a.seq_qstart[b];
     const int t0 = chunk * a.chunk_len, t1 = min(qlen, t0 + a.chunk_len);
     if (t0 >= qlen) return;
-    float* as = smem;                                 // [TOKENS][D] decay (bounded forget; the gated kind's is a scalar)
+    constexpr bool SCALAR = KIND == 0 || KIND == 3;   // one decay for all rows of a (token, head)
+    float* as = smem;                                 // [TOKENS][D] decay (bounded forget; the other kinds' is a scalar)
     float* bs = as + MC_TOKENS * D;                   // [TOKENS][D] input per row
     float* qs = bs + MC_TOKENS * D;                   // [TOKENS][D]
-    float* vs = qs + MC_TOKENS * D;                   // [TOKENS][MC_THREADS]
-    float* ks = vs + MC_TOKENS * MC_THREADS;          // [TOKENS] the gated kind's keep
+    float* vs = qs + MC_TOKENS * D;                   // [TOKENS][NT]
+    float* ks = vs + MC_TOKENS * NT;                  // [TOKENS] the scalar keep
+    float* ts = ks + MC_TOKENS;                       // [TOKENS] the plain decay's take
+    const int kh = KIND == 3 ? h / (H / a.KVH) : h;   // the head of q and k this head reads
     float* cs = a.chunk_state + ((((size_t)b * a.n_chunks + chunk) * H + h) * D) * cols;
     float S[DMAX];
 #pragma unroll
@@ -1006,13 +1041,29 @@ memory_chunk_walk_kernel(MemoryChunkArgs a) {
         const int ns = min(MC_TOKENS, t1 - s0);
         __syncthreads();
 #pragma unroll 4
-        for (int e = threadIdx.x; e < ns * D; e += MC_THREADS) {
+        for (int e = threadIdx.x; e < ns * D; e += NT) {
             const int s = e / D, d = e - s * D;
             const size_t t = (size_t)(qstart + s0 + s);
             const TA* row = (const TA*)a.proj + t * a.ld;
             if (KIND == 0) {
                 bs[e] = a.gates[(t * H + h) * 4 + 1] * gl_load(row + a.k_off + h * D + d);
                 if (MODE == 2) qs[e] = gl_load(row + a.q_off + h * D + d) * a.q_scale;
+            } else if (KIND == 3) {
+                float kv = gl_load(row + a.k_off + kh * D + d), qv = MODE == 2 ? gl_load(row + a.q_off + kh * D + d) : 0.f;
+                if (a.cosv && d < 2 * a.rot_half) {
+                    // the pair (u, v) = (dim i, dim i + rot_half) becomes (u c - v s, v c + u s)
+                    const bool first = d < a.rot_half;
+                    const int i = first ? d : d - a.rot_half, other = first ? d + a.rot_half : d - a.rot_half;
+                    const float c = a.cosv[t * a.rot_half + i], sn = a.sinv[t * a.rot_half + i];
+                    const float ko = gl_load(row + a.k_off + kh * D + other);
+                    kv = first ? kv * c - ko * sn : kv * c + ko * sn;
+                    if (MODE == 2) {
+                        const float qo = gl_load(row + a.q_off + kh * D + other);
+                        qv = first ? qv * c - qo * sn : qv * c + qo * sn;
+                    }
+                }
+                bs[e] = kv * a.k_scale;
+                if (MODE == 2) qs[e] = qv * a.q_scale;
             } else {
                 const float l = a.lower[h * D + d];
                 const float f = l + (1.0f - l) * rc_sigmoid(gl_load(row + a.f_off + h * D + d));
@@ -1021,16 +1072,21 @@ memory_chunk_walk_kernel(MemoryChunkArgs a) {
                 if (MODE == 2) qs[e] = rc_silu(gl_load(row + a.q_off + h * D + d));
             }
         }
-        for (int e = threadIdx.x; e < ns * MC_THREADS; e += MC_THREADS) {
-            const int s = e / MC_THREADS, j = col0 + (e - s * MC_THREADS);
+        for (int e = threadIdx.x; e < ns * NT; e += NT) {
+            const int s = e / NT, j = col0 + (e - s * NT);
             const TA* row = (const TA*)a.proj + (size_t)(qstart + s0 + s) * a.ld;
             vs[e] = j < V ? gl_load(row + a.v_off + h * V + j) : 1.0f;     // the normaliser's column takes 1
         }
-        if (KIND == 0 && threadIdx.x < ns) ks[threadIdx.x] = a.gates[((size_t)(qstart + s0 + threadIdx.x) * H + h) * 4];
+        if (SCALAR && threadIdx.x < ns) {
+            const float* g = a.gates + ((size_t)(qstart + s0 + threadIdx.x) * H + h) * 4;
+            ks[threadIdx.x] = g[0];
+            if (KIND == 3) ts[threadIdx.x] = g[1];
+        }
         __syncthreads();
         for (int s = 0; s < ns; ++s) {
-            const float v = vs[s * MC_THREADS + threadIdx.x];
-            const float keep = KIND == 0 ? ks[s] : 0.f;
+            const float v_in = vs[s * NT + threadIdx.x];
+            const float v = KIND == 3 ? ts[s] * v_in : v_in;
+            const float keep = SCALAR ? ks[s] : 0.f;
             const float* ar = as + s * D;
             const float* br = bs + s * D;
             const float* qr = qs + s * D;
@@ -1038,12 +1094,13 @@ memory_chunk_walk_kernel(MemoryChunkArgs a) {
 #pragma unroll
             for (int d = 0; d < DMAX; ++d) {
                 if (d < D) {
-                    S[d] = fmaf(KIND == 0 ? keep : ar[d], S[d], br[d] * v);
+                    S[d] = fmaf(SCALAR ? keep : ar[d], S[d], br[d] * v);
                     if (MODE == 2) num = fmaf(S[d], qr[d], num);
                 }
             }
             if (MODE == 2 && live) {
                 const size_t t = (size_t)(qstart + s0 + s);
+                if (KIND == 3 && a.d_skip) num = fmaf(a.d_skip[h], v_in, num);
                 if (col < V) a.out[t * H * V + (size_t)h * V + col] = num;
                 else a.nq[t * H + h] = num;
             }
@@ -1099,30 +1156,42 @@ memory_divide_kernel(MemoryChunkArgs a) {
     }
 }
 
-template <typename TA, int DMAX, int KIND>
-static int launch_memory_chunks(const MemoryChunkArgs& a, cudaStream_t stream) {
-    const size_t smem = (size_t)MC_TOKENS * (3 * a.D + MC_THREADS + 1) * sizeof(float);
+template <typename TA, int DMAX, int KIND, int NT>
+static int launch_memory_chunks_nt(const MemoryChunkArgs& a, cudaStream_t stream) {
+    const size_t smem = (size_t)MC_TOKENS * (3 * a.D + NT + 2) * sizeof(float);
     if (smem > 48 * 1024) return GL_ERR_SMEM;
-    const dim3 walk((a.cols + MC_THREADS - 1) / MC_THREADS, a.H, a.B * a.n_chunks);
+    const dim3 walk((a.cols + NT - 1) / NT, a.H, a.B * a.n_chunks);
     int rc;
-    if (KIND == 0) {
+    if (KIND == 0 || KIND == 3) {
         const long long n = (long long)a.T * a.H;
-        rc = gl_launch(memory_log_gates_kernel<TA>, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, stream, 1, a);
+        if (KIND == 0) rc = gl_launch(memory_log_gates_kernel<TA>, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, stream, 1, a);
+        else rc = gl_launch(memory_decay_gates_kernel<TA>, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, stream, 1, a);
         if (rc != 0) return rc;
+    }
+    if (KIND == 0) {
         rc = gl_launch(memory_gate_walk_kernel, dim3(a.B * a.H), dim3(32), 0, stream, 1, a);
         if (rc != 0) return rc;
     }
     rc = gl_launch(memory_chunk_decay_kernel<TA, KIND>, dim3((a.D + 127) / 128, a.H, a.B * a.n_chunks), dim3(128), 0, stream, 1, a);
     if (rc != 0) return rc;
-    rc = gl_launch_in_order(memory_chunk_walk_kernel<TA, DMAX, KIND, 1>, walk, dim3(MC_THREADS), smem, stream, a);
+    rc = gl_launch_in_order(memory_chunk_walk_kernel<TA, DMAX, KIND, 1, NT>, walk, dim3(NT), smem, stream, a);
     if (rc != 0) return rc;
     rc = gl_launch(memory_chunk_carry_kernel, dim3((a.D * a.cols + 127) / 128, a.H, a.B), dim3(128), 0, stream, 1, a);
     if (rc != 0) return rc;
-    rc = gl_launch_in_order(memory_chunk_walk_kernel<TA, DMAX, KIND, 2>, walk, dim3(MC_THREADS), smem, stream, a);
+    rc = gl_launch_in_order(memory_chunk_walk_kernel<TA, DMAX, KIND, 2, NT>, walk, dim3(NT), smem, stream, a);
     if (rc != 0 || KIND != 0) return rc;
     const long long n = (long long)a.T * a.H * a.V;
     const long long want = (n + 255) / 256;
     return gl_launch(memory_divide_kernel, dim3((unsigned)(want > 16384 ? 16384 : want)), dim3(256), 0, stream, 1, a);
+}
+
+template <typename TA, int DMAX, int KIND>
+static int launch_memory_chunks(const MemoryChunkArgs& a, cudaStream_t stream) {
+    // heads of up to 64 columns (a state-space layer's) would leave half of a block's threads without a column
+    if constexpr (KIND == 3) {
+        if (a.cols <= 64) return launch_memory_chunks_nt<TA, DMAX, KIND, 64>(a, stream);
+    }
+    return launch_memory_chunks_nt<TA, DMAX, KIND, MC_THREADS>(a, stream);
 }
 
 template <typename TA, int KIND>
@@ -1134,16 +1203,28 @@ static int dispatch_memory_chunks(const MemoryChunkArgs& a, cudaStream_t stream)
     return GL_ERR_SHAPE;
 }
 
-// (launches 4 kernels for the bounded-forget kind, 7 for the gated one)
+template <typename TA>
+static int dispatch_memory_chunks_kind(const MemoryChunkArgs& a, cudaStream_t stream) {
+    if (a.kind == 0) return dispatch_memory_chunks<TA, 0>(a, stream);
+    if (a.kind == 1) return dispatch_memory_chunks<TA, 1>(a, stream);
+    return dispatch_memory_chunks<TA, 3>(a, stream);
+}
+
+// (launches 4 kernels for the bounded-forget kind, 5 for the plain decay, 7 for the gated one)
 GL_API int gl_memory_chunks(const MemoryChunkArgs* args, int act_dtype, cudaStream_t stream) {
     const MemoryChunkArgs& a = *args;
     if (a.B <= 0 || a.T <= 0) return GL_OK;
     if (a.H <= 0 || a.D <= 0 || a.D > 128 || a.V <= 0 || a.n_chunks <= 0 || a.chunk_len <= 0) return GL_ERR_SHAPE;
-    if ((a.kind != 0 && a.kind != 1) || a.cols != a.V + (a.kind == 0 ? 1 : 0)) return GL_ERR_SHAPE;
+    if ((a.kind != 0 && a.kind != 1 && a.kind != 3) || a.cols != a.V + (a.kind == 0 ? 1 : 0)) return GL_ERR_SHAPE;
     if ((long long)a.B * a.n_chunks > 65535 || a.H > 65535) return GL_ERR_SHAPE;
     if (!a.chunk_state || !a.chunk_decay || (a.kind == 0 && (!a.nq || !a.gates || !(a.cap > 0.f)))) return GL_ERR_SHAPE;
-    if (act_dtype == GL_F32) return a.kind == 0 ? dispatch_memory_chunks<float, 0>(a, stream) : dispatch_memory_chunks<float, 1>(a, stream);
-    if (act_dtype == GL_BF16)
-        return a.kind == 0 ? dispatch_memory_chunks<__nv_bfloat16, 0>(a, stream) : dispatch_memory_chunks<__nv_bfloat16, 1>(a, stream);
+    if (a.kind == 3) {
+        if (!a.gates || a.KVH <= 0 || a.H % a.KVH) return GL_ERR_SHAPE;
+        if ((a.lower != nullptr) == (a.gates_in != nullptr)) return GL_ERR_SHAPE;
+        if (a.gates_in && (!a.a_log || !a.dt_bias)) return GL_ERR_SHAPE;
+        if (a.cosv && (!a.sinv || a.rot_half <= 0 || 2 * a.rot_half > a.D)) return GL_ERR_SHAPE;
+    }
+    if (act_dtype == GL_F32) return dispatch_memory_chunks_kind<float>(a, stream);
+    if (act_dtype == GL_BF16) return dispatch_memory_chunks_kind<__nv_bfloat16>(a, stream);
     return GL_ERR_DTYPE;
 }

@@ -1010,7 +1010,10 @@ class _MemoryChunkArgs(Structure):
                 ("T", c_int), ("ld", c_int), ("q_off", c_int), ("k_off", c_int), ("v_off", c_int), ("i_off", c_int),
                 ("f_off", c_int), ("B", c_int), ("H", c_int), ("D", c_int), ("V", c_int), ("cols", c_int),
                 ("state_stride", c_int), ("kind", c_int), ("chunk_len", c_int), ("n_chunks", c_int),
-                ("cap", c_float), ("q_scale", c_float)]
+                ("cap", c_float), ("q_scale", c_float),
+                ("gates_in", c_void_p), ("a_log", c_void_p), ("dt_bias", c_void_p), ("cosv", c_void_p),
+                ("sinv", c_void_p), ("d_skip", c_void_p), ("gates_ld", c_int), ("KVH", c_int), ("rot_half", c_int),
+                ("k_scale", c_float)]
 
 
 MEMORY_CHUNKS_MAX_ROWS = 128     # rows a head the chunked walk of the matrix memories takes (a column's rows in registers)
@@ -1072,23 +1075,29 @@ def memory_scan(kind: int, proj: torch.Tensor, state: torch.Tensor, ctx, H: int,
     if kind == MEMORY_BOUNDED_FORGET:
         _need(lower, "lower", torch.float32, (H * D,))
     out = empty((T, H * V), torch.float32, proj.device)
-    if (USE_MEMORY_CHUNKS and kind in (MEMORY_GATED, MEMORY_BOUNDED_FORGET) and ctx.max_qlen >= SCAN_CHUNKED_FROM
-            and D <= MEMORY_CHUNKS_MAX_ROWS):
+    if (USE_MEMORY_CHUNKS and kind in (MEMORY_GATED, MEMORY_BOUNDED_FORGET, MEMORY_DECAY)
+            and ctx.max_qlen >= SCAN_CHUNKED_FROM and D <= MEMORY_CHUNKS_MAX_ROWS):
         # a long run: chunks of tokens side by side, a lane a column (two walks and a carry between them)
-        gated = kind == MEMORY_GATED
+        gated, plain = kind == MEMORY_GATED, kind == MEMORY_DECAY
         chunks = -(-ctx.max_qlen // SCAN_CHUNK_TOKENS)
         cols = V + (1 if gated else 0)
         chunk_state = empty((ctx.n_seqs, chunks, H, D, cols), torch.float32, proj.device)
         chunk_decay = empty((ctx.n_seqs, chunks, H, D), torch.float32, proj.device)
         nq = empty((T, H), torch.float32, proj.device) if gated else None
-        gates = empty((T, H, 4), torch.float32, proj.device) if gated else None
-        c = _MemoryChunkArgs(proj.data_ptr(), out.data_ptr(), _addr(nq), _addr(gates), state.data_ptr(), _addr(lower),
+        scratch = empty((T, H, 4), torch.float32, proj.device) if gated or plain else None
+        c = _MemoryChunkArgs(proj.data_ptr(), out.data_ptr(), _addr(nq), _addr(scratch), state.data_ptr(), _addr(lower),
                              chunk_state.data_ptr(), chunk_decay.data_ptr(), ctx.tok_seq.data_ptr(),
                              ctx.seq_slot.data_ptr(), ctx.seq_qstart.data_ptr(), ctx.seq_qlen.data_ptr(),
                              T, ld, q_off, k_off, v_off, i_off, f_off, ctx.n_seqs, H, D, V, cols, state.shape[1], kind,
-                             SCAN_CHUNK_TOKENS, chunks, cap, q_scale)
+                             SCAN_CHUNK_TOKENS, chunks, cap, q_scale,
+                             _addr(gates) if plain else None, _addr(a_log) if plain else None,
+                             _addr(dt_bias) if plain else None, _addr(cos) if rot_half else None,
+                             _addr(sin) if rot_half else None, _addr(skip) if plain else None,
+                             gates.shape[1] if plain and gates is not None else 0, kv_heads if plain else 0, rot_half,
+                             k_scale)
         fn = _lib("recurrent.cu").gl_memory_chunks
-        _check(_launch(fn, byref(c), c_int(dtype_code(proj.dtype)), _stream()), "memory_chunks", 7 if gated else 4)
+        _check(_launch(fn, byref(c), c_int(dtype_code(proj.dtype)), _stream()), "memory_chunks",
+               7 if gated else 5 if plain else 4)
         return out
     # the gated kind's new normaliser and maximum, moved into the state rows by a second kernel
     nm = empty((ctx.n_seqs, H, D + 1), torch.float32, proj.device) if kind == MEMORY_GATED else None
