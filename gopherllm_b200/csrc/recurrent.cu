@@ -1012,8 +1012,46 @@ memory_chunk_decay_kernel(MemoryChunkArgs a) {
     a.chunk_decay[(((size_t)b * a.n_chunks + chunk) * a.H + h) * a.D + d] = p;
 }
 
+// 16 bytes of a row (4 floats or 8 bfloat16) as floats into shared memory; both addresses 16-byte aligned
+__device__ __forceinline__ void mc_load16(const float* src, float* dst) {
+    *reinterpret_cast<float4*>(dst) = *reinterpret_cast<const float4*>(src);
+}
+__device__ __forceinline__ void mc_load16(const __nv_bfloat16* src, float* dst) {
+    const uint4 raw = *reinterpret_cast<const uint4*>(src);
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+    const float2 f0 = __bfloat1622float2(h[0]), f1 = __bfloat1622float2(h[1]);
+    const float2 f2 = __bfloat1622float2(h[2]), f3 = __bfloat1622float2(h[3]);
+    reinterpret_cast<float4*>(dst)[0] = make_float4(f0.x, f0.y, f1.x, f1.y);
+    reinterpret_cast<float4*>(dst)[1] = make_float4(f2.x, f2.y, f3.x, f3.y);
+}
+
+// two 32-bit multiply-adds in one instruction (the pair's halves are independent and rounded like fmaf's)
+__device__ __forceinline__ unsigned long long mc_pack(float x, float y) {
+    unsigned long long r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(x), "f"(y));
+    return r;
+}
+__device__ __forceinline__ unsigned long long mc_fma2(unsigned long long a, unsigned long long b, unsigned long long c) {
+    unsigned long long r;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+    return r;
+}
+__device__ __forceinline__ unsigned long long mc_mul2(unsigned long long a, unsigned long long b) {
+    unsigned long long r;
+    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+    return r;
+}
+__device__ __forceinline__ float2 mc_unpack(unsigned long long v) {
+    float2 r;
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(r.x), "=f"(r.y) : "l"(v));
+    return r;
+}
+
 // MODE 1: from zero, keep the last state.  MODE 2: from the chunk's start, with outputs.  NT: threads (columns) a block.
-template <typename TA, int DMAX, int KIND, int MODE, int NT>
+// FULL: D == DMAX, so no row needs a bounds check; a token's rows are then read four at a time and updated in
+// pairs (fma.rn.f32x2), and the read-out is summed in four parts (the walk issues less than half the
+// instructions a row that the checked form does, which is what bounds it).
+template <typename TA, int DMAX, int KIND, int MODE, int NT, bool FULL>
 __global__ void __launch_bounds__(NT)
 memory_chunk_walk_kernel(MemoryChunkArgs a) {
     extern __shared__ __align__(16) float smem[];
@@ -1033,6 +1071,10 @@ memory_chunk_walk_kernel(MemoryChunkArgs a) {
     float* ks = vs + MC_TOKENS * NT;                  // [TOKENS] the scalar keep
     float* ts = ks + MC_TOKENS;                       // [TOKENS] the plain decay's take
     const int kh = KIND == 3 ? h / (H / a.KVH) : h;   // the head of q and k this head reads
+    constexpr int VEC = 16 / (int)sizeof(TA);
+    // rows of whole, aligned 16-byte pieces can be fetched as such
+    const bool wide = KIND == 3 && D % VEC == 0 && V % VEC == 0 && a.ld % VEC == 0 && a.q_off % VEC == 0
+                      && a.k_off % VEC == 0 && a.v_off % VEC == 0 && ((size_t)a.proj & 15) == 0;
     float* cs = a.chunk_state + ((((size_t)b * a.n_chunks + chunk) * H + h) * D) * cols;
     float S[DMAX];
 #pragma unroll
@@ -1040,42 +1082,81 @@ memory_chunk_walk_kernel(MemoryChunkArgs a) {
     for (int s0 = t0; s0 < t1; s0 += MC_TOKENS) {
         const int ns = min(MC_TOKENS, t1 - s0);
         __syncthreads();
-#pragma unroll 4
-        for (int e = threadIdx.x; e < ns * D; e += NT) {
-            const int s = e / D, d = e - s * D;
-            const size_t t = (size_t)(qstart + s0 + s);
-            const TA* row = (const TA*)a.proj + t * a.ld;
-            if (KIND == 0) {
-                bs[e] = a.gates[(t * H + h) * 4 + 1] * gl_load(row + a.k_off + h * D + d);
-                if (MODE == 2) qs[e] = gl_load(row + a.q_off + h * D + d) * a.q_scale;
-            } else if (KIND == 3) {
-                float kv = gl_load(row + a.k_off + kh * D + d), qv = MODE == 2 ? gl_load(row + a.q_off + kh * D + d) : 0.f;
-                if (a.cosv && d < 2 * a.rot_half) {
-                    // the pair (u, v) = (dim i, dim i + rot_half) becomes (u c - v s, v c + u s)
-                    const bool first = d < a.rot_half;
-                    const int i = first ? d : d - a.rot_half, other = first ? d + a.rot_half : d - a.rot_half;
-                    const float c = a.cosv[t * a.rot_half + i], sn = a.sinv[t * a.rot_half + i];
-                    const float ko = gl_load(row + a.k_off + kh * D + other);
-                    kv = first ? kv * c - ko * sn : kv * c + ko * sn;
-                    if (MODE == 2) {
-                        const float qo = gl_load(row + a.q_off + kh * D + other);
-                        qv = first ? qv * c - qo * sn : qv * c + qo * sn;
+        if (KIND == 3 && wide) {
+            // whole 16-byte pieces of the rows first, as they are; then rotation and scale in place
+            const int DV = D / VEC;
+            for (int e = threadIdx.x; e < ns * DV; e += NT) {
+                const int s = e / DV, d = (e - s * DV) * VEC;
+                const TA* row = (const TA*)a.proj + (size_t)(qstart + s0 + s) * a.ld;
+                mc_load16(row + a.k_off + kh * D + d, bs + s * D + d);
+                if (MODE == 2) mc_load16(row + a.q_off + kh * D + d, qs + s * D + d);
+            }
+            for (int e = threadIdx.x; e < ns * (NT / VEC); e += NT) {
+                const int s = e / (NT / VEC), j = (e - s * (NT / VEC)) * VEC;
+                const TA* row = (const TA*)a.proj + (size_t)(qstart + s0 + s) * a.ld;
+                if (col0 + j < V) mc_load16(row + a.v_off + h * V + col0 + j, vs + s * NT + j);   // (V is whole pieces)
+            }
+            if (a.cosv || a.k_scale != 1.0f || (MODE == 2 && a.q_scale != 1.0f)) {
+                __syncthreads();
+                const int half = a.cosv ? a.rot_half : 0;
+                for (int e = threadIdx.x; e < ns * D; e += NT) {
+                    const int s = e / D, d = e - s * D;
+                    if (d < half) {
+                        // the pair (u, v) = (dim d, dim d + half) becomes (u c - v s, v c + u s)
+                        const size_t t = (size_t)(qstart + s0 + s);
+                        const float c = a.cosv[t * half + d], sn = a.sinv[t * half + d];
+                        const float ku = bs[e], kv = bs[e + half];
+                        bs[e] = (ku * c - kv * sn) * a.k_scale;
+                        bs[e + half] = (kv * c + ku * sn) * a.k_scale;
+                        if (MODE == 2) {
+                            const float qu = qs[e], qv = qs[e + half];
+                            qs[e] = (qu * c - qv * sn) * a.q_scale;
+                            qs[e + half] = (qv * c + qu * sn) * a.q_scale;
+                        }
+                    } else if (d >= 2 * half) {
+                        bs[e] *= a.k_scale;
+                        if (MODE == 2) qs[e] *= a.q_scale;
                     }
                 }
-                bs[e] = kv * a.k_scale;
-                if (MODE == 2) qs[e] = qv * a.q_scale;
-            } else {
-                const float l = a.lower[h * D + d];
-                const float f = l + (1.0f - l) * rc_sigmoid(gl_load(row + a.f_off + h * D + d));
-                as[e] = f;
-                bs[e] = 1.0f - f;
-                if (MODE == 2) qs[e] = rc_silu(gl_load(row + a.q_off + h * D + d));
             }
-        }
-        for (int e = threadIdx.x; e < ns * NT; e += NT) {
-            const int s = e / NT, j = col0 + (e - s * NT);
-            const TA* row = (const TA*)a.proj + (size_t)(qstart + s0 + s) * a.ld;
-            vs[e] = j < V ? gl_load(row + a.v_off + h * V + j) : 1.0f;     // the normaliser's column takes 1
+        } else {
+    #pragma unroll 4
+            for (int e = threadIdx.x; e < ns * D; e += NT) {
+                const int s = e / D, d = e - s * D;
+                const size_t t = (size_t)(qstart + s0 + s);
+                const TA* row = (const TA*)a.proj + t * a.ld;
+                if (KIND == 0) {
+                    bs[e] = a.gates[(t * H + h) * 4 + 1] * gl_load(row + a.k_off + h * D + d);
+                    if (MODE == 2) qs[e] = gl_load(row + a.q_off + h * D + d) * a.q_scale;
+                } else if (KIND == 3) {
+                    float kv = gl_load(row + a.k_off + kh * D + d), qv = MODE == 2 ? gl_load(row + a.q_off + kh * D + d) : 0.f;
+                    if (a.cosv && d < 2 * a.rot_half) {
+                        // the pair (u, v) = (dim i, dim i + rot_half) becomes (u c - v s, v c + u s)
+                        const bool first = d < a.rot_half;
+                        const int i = first ? d : d - a.rot_half, other = first ? d + a.rot_half : d - a.rot_half;
+                        const float c = a.cosv[t * a.rot_half + i], sn = a.sinv[t * a.rot_half + i];
+                        const float ko = gl_load(row + a.k_off + kh * D + other);
+                        kv = first ? kv * c - ko * sn : kv * c + ko * sn;
+                        if (MODE == 2) {
+                            const float qo = gl_load(row + a.q_off + kh * D + other);
+                            qv = first ? qv * c - qo * sn : qv * c + qo * sn;
+                        }
+                    }
+                    bs[e] = kv * a.k_scale;
+                    if (MODE == 2) qs[e] = qv * a.q_scale;
+                } else {
+                    const float l = a.lower[h * D + d];
+                    const float f = l + (1.0f - l) * rc_sigmoid(gl_load(row + a.f_off + h * D + d));
+                    as[e] = f;
+                    bs[e] = 1.0f - f;
+                    if (MODE == 2) qs[e] = rc_silu(gl_load(row + a.q_off + h * D + d));
+                }
+            }
+            for (int e = threadIdx.x; e < ns * NT; e += NT) {
+                const int s = e / NT, j = col0 + (e - s * NT);
+                const TA* row = (const TA*)a.proj + (size_t)(qstart + s0 + s) * a.ld;
+                vs[e] = j < V ? gl_load(row + a.v_off + h * V + j) : 1.0f;     // the normaliser's column takes 1
+            }
         }
         if (SCALAR && threadIdx.x < ns) {
             const float* g = a.gates + ((size_t)(qstart + s0 + threadIdx.x) * H + h) * 4;
@@ -1091,11 +1172,40 @@ memory_chunk_walk_kernel(MemoryChunkArgs a) {
             const float* br = bs + s * D;
             const float* qr = qs + s * D;
             float num = 0.f;
+            if constexpr (FULL) {
+                const unsigned long long v2 = mc_pack(v, v), keep2 = mc_pack(keep, keep);
+                unsigned long long n01 = mc_pack(0.f, 0.f), n23 = n01;
 #pragma unroll
-            for (int d = 0; d < DMAX; ++d) {
-                if (d < D) {
-                    S[d] = fmaf(SCALAR ? keep : ar[d], S[d], br[d] * v);
-                    if (MODE == 2) num = fmaf(S[d], qr[d], num);
+                for (int d = 0; d < DMAX; d += 4) {
+                    const float4 b4 = *reinterpret_cast<const float4*>(br + d);
+                    unsigned long long a01 = keep2, a23 = keep2;
+                    if (!SCALAR) {
+                        const float4 a4 = *reinterpret_cast<const float4*>(ar + d);
+                        a01 = mc_pack(a4.x, a4.y);
+                        a23 = mc_pack(a4.z, a4.w);
+                    }
+                    unsigned long long s01 = mc_pack(S[d], S[d + 1]), s23 = mc_pack(S[d + 2], S[d + 3]);
+                    s01 = mc_fma2(a01, s01, mc_mul2(mc_pack(b4.x, b4.y), v2));
+                    s23 = mc_fma2(a23, s23, mc_mul2(mc_pack(b4.z, b4.w), v2));
+                    if (MODE == 2) {
+                        const float4 q4 = *reinterpret_cast<const float4*>(qr + d);
+                        n01 = mc_fma2(s01, mc_pack(q4.x, q4.y), n01);
+                        n23 = mc_fma2(s23, mc_pack(q4.z, q4.w), n23);
+                    }
+                    const float2 r01 = mc_unpack(s01), r23 = mc_unpack(s23);
+                    S[d] = r01.x; S[d + 1] = r01.y; S[d + 2] = r23.x; S[d + 3] = r23.y;
+                }
+                if (MODE == 2) {
+                    const float2 p01 = mc_unpack(n01), p23 = mc_unpack(n23);
+                    num = (p01.x + p01.y) + (p23.x + p23.y);
+                }
+            } else {
+#pragma unroll
+                for (int d = 0; d < DMAX; ++d) {
+                    if (d < D) {
+                        S[d] = fmaf(SCALAR ? keep : ar[d], S[d], br[d] * v);
+                        if (MODE == 2) num = fmaf(S[d], qr[d], num);
+                    }
                 }
             }
             if (MODE == 2 && live) {
@@ -1174,11 +1284,14 @@ static int launch_memory_chunks_nt(const MemoryChunkArgs& a, cudaStream_t stream
     }
     rc = gl_launch(memory_chunk_decay_kernel<TA, KIND>, dim3((a.D + 127) / 128, a.H, a.B * a.n_chunks), dim3(128), 0, stream, 1, a);
     if (rc != 0) return rc;
-    rc = gl_launch_in_order(memory_chunk_walk_kernel<TA, DMAX, KIND, 1, NT>, walk, dim3(NT), smem, stream, a);
+    const bool full = a.D == DMAX;
+    rc = full ? gl_launch_in_order(memory_chunk_walk_kernel<TA, DMAX, KIND, 1, NT, true>, walk, dim3(NT), smem, stream, a)
+              : gl_launch_in_order(memory_chunk_walk_kernel<TA, DMAX, KIND, 1, NT, false>, walk, dim3(NT), smem, stream, a);
     if (rc != 0) return rc;
     rc = gl_launch(memory_chunk_carry_kernel, dim3((a.D * a.cols + 127) / 128, a.H, a.B), dim3(128), 0, stream, 1, a);
     if (rc != 0) return rc;
-    rc = gl_launch_in_order(memory_chunk_walk_kernel<TA, DMAX, KIND, 2, NT>, walk, dim3(NT), smem, stream, a);
+    rc = full ? gl_launch_in_order(memory_chunk_walk_kernel<TA, DMAX, KIND, 2, NT, true>, walk, dim3(NT), smem, stream, a)
+              : gl_launch_in_order(memory_chunk_walk_kernel<TA, DMAX, KIND, 2, NT, false>, walk, dim3(NT), smem, stream, a);
     if (rc != 0 || KIND != 0) return rc;
     const long long n = (long long)a.T * a.H * a.V;
     const long long want = (n + 255) / 256;
