@@ -178,26 +178,33 @@ def lilupel_model_spec(cfg: LilupelConfig) -> ModelSpec:
     norm = NormSpec("rmsnorm", cfg.width, cfg.norm_eps, bias=False, weight_offset=1.0)
     layers, schedule = [], []
     block_of = {}                    # layer of the file -> index of its block
+    n = len(cfg.layers)
     for i, L in enumerate(cfg.layers):
         where = f"layers[{i}]"
         if not isinstance(L, dict) or L.get("type") not in _MIXERS:
             raise ValueError(f"config.json: {where}.type must be one of {', '.join(sorted(_MIXERS))}")
-        source = L.get("weights_of")
-        if source is not None:
-            if isinstance(source, bool) or not isinstance(source, int) or source not in block_of:
-                raise ValueError(f"config.json: {where}.weights_of must name an earlier layer with tensors of its own, "
-                                 f"is {source!r}")
-            theirs = cfg.layers[source]
-            if any(theirs.get(k) != L.get(k) for k in ("type", "mixer", "mlp")):
-                raise ValueError(f"config.json: {where} runs on layer {source}'s weights but its entry differs")
-            schedule.append(ScheduleEntry(layer=block_of[source], cache=i))
+        if L.get("weights_of") is not None:
             continue
         mixer = _MIXERS[L["type"]](cfg, _object(where, L, "mixer"), where + ".mixer")
         ffn = _feed_forward(cfg, L.get("mlp"), where + ".mlp")
         block_of[i] = len(layers)
         layers.append(BlockSpec(arrangement="post_norm", norm=norm, mixer=mixer, ffn=ffn,
                                 norm2=norm if ffn is not None else None))
-        schedule.append(ScheduleEntry(layer=block_of[i], cache=i))
+    for i, L in enumerate(cfg.layers):
+        where = f"layers[{i}]"
+        source, hops = i, 0
+        while cfg.layers[source].get("weights_of") is not None:       # a layer may name one that names another
+            nxt = cfg.layers[source]["weights_of"]
+            hops += 1
+            if isinstance(nxt, bool) or not isinstance(nxt, int) or not 0 <= nxt < n or nxt == source or hops > n:
+                raise ValueError(f"config.json: {where}.weights_of must lead to a layer with tensors of its own, "
+                                 f"is {L.get('weights_of')!r}")
+            source = nxt
+        if source != i:
+            theirs = cfg.layers[source]
+            if any(theirs.get(k) != L.get(k) for k in ("type", "mixer", "mlp")):
+                raise ValueError(f"config.json: {where} runs on layer {source}'s weights but its entry differs")
+        schedule.append(ScheduleEntry(layer=block_of[source], cache=i))
     return ModelSpec(hidden=cfg.width, vocab=cfg.vocab, max_positions=UNBOUNDED_POSITIONS, layers=tuple(layers),
                      schedule=tuple(schedule), final_norm=norm, tie_embeddings=True, head_bias=False)
 

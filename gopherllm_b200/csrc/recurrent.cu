@@ -1245,12 +1245,23 @@ memory_chunk_carry_kernel(MemoryChunkArgs a) {
     const float* srow = a.state + (size_t)a.seq_slot[b] * a.state_stride;
     float S = col < a.V ? srow[((size_t)h * a.D + d) * a.V + col] : srow[(size_t)a.H * a.D * a.V + (size_t)h * a.D + d];
     const int chunks = (a.seq_qlen[b] + a.chunk_len - 1) / a.chunk_len;
-    for (int k = 0; k < chunks; ++k) {
-        const size_t at = ((size_t)b * a.n_chunks + k) * a.H + h;
-        float* slot = a.chunk_state + (at * a.D + d) * a.cols + col;
-        const float last = *slot;
-        *slot = S;
-        S = fmaf(a.chunk_decay[at * a.D + d], S, last);
+    // eight chunks' last states and decays are asked for at once, so that a chunk costs no trip to memory of its own
+    for (int k0 = 0; k0 < chunks; k0 += 8) {
+        float last[8], decay[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const size_t at = ((size_t)b * a.n_chunks + min(k0 + j, chunks - 1)) * a.H + h;
+            last[j] = a.chunk_state[(at * a.D + d) * a.cols + col];
+            decay[j] = a.chunk_decay[at * a.D + d];
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            if (k0 + j < chunks) {
+                const size_t at = ((size_t)b * a.n_chunks + k0 + j) * a.H + h;
+                a.chunk_state[(at * a.D + d) * a.cols + col] = S;
+                S = fmaf(decay[j], S, last[j]);
+            }
+        }
     }
 }
 

@@ -87,6 +87,22 @@ def test_layers_that_run_on_another_layers_weights():
     assert cache.open() == s and float(cache.view(2).rows[s].abs().max()) == 0.0
 
 
+def test_weights_of_a_later_layer_and_of_a_layer_that_names_another():
+    cfg = copy.deepcopy(lm.ALPHA)
+    del cfg["layers"][3]["weights_of"]
+    cfg["layers"][1]["weights_of"] = 3                 # the owner comes after its user
+    arch, typed, model = build(cfg)
+    assert [(e.layer, e.cache) for e in model.spec.schedule] == [(0, 0), (2, 1), (1, 2), (2, 3)]
+    names = arch.tensor_names(typed)
+    assert names.layer(2, "norm", "weight") == "l3.norm1" and names.layer(1, "mixer", "in.weight") == "l2.mix.in"
+    cfg["layers"].append(dict(copy.deepcopy(cfg["layers"][1]), weights_of=1))     # 4 -> 1 -> 3
+    _, _, chained = build(cfg)
+    assert [(e.layer, e.cache) for e in chained.spec.schedule][-1] == (2, 4)
+    cfg["layers"][3]["weights_of"] = 4                 # 3 -> 4 -> 1 -> 3: nobody has the tensors
+    with pytest.raises(ValueError):
+        build(cfg)
+
+
 def _with(cfg, path, value):
     out = copy.deepcopy(cfg)
     at = out
