@@ -348,8 +348,9 @@ def test_long_runs_walked_as_chunks(dtype, monkeypatch):
     walks.  With chunks of 16 tokens from 32 tokens on: a whole prompt (a ragged last chunk), pieces above and
     below the threshold that go on from a state, and a batch whose shorter sequence has fewer chunks."""
     from gopherllm_b200 import ops
-    monkeypatch.setattr(ops, "SCAN_CHUNK_TOKENS", 16)
-    monkeypatch.setattr(ops, "SCAN_CHUNKED_FROM", 32)
+    monkeypatch.setattr(ops, "DECAY_CHUNK_TOKENS", 16)
+    monkeypatch.setattr(ops, "DECAY_CHUNK_TOKENS_SHORT", 16)
+    monkeypatch.setattr(ops, "DECAY_CHUNKED_FROM", 32)
     for cfg_name, cfg in (("ALPHA", lm.ALPHA), ("BETA", lm.BETA), ("GAMMA", lm.GAMMA), ("WIDE", WIDE)):
         folder = folder_for(cfg_name, cfg, 5, long_memory=True)
         toks = tokens_for(cfg, 150, 2)
