@@ -576,6 +576,33 @@ GL_API int gl_head_norm_gate(const float* o, const float* w, const void* gate, v
     return GL_ERR_DTYPE;
 }
 
+// 16 bytes of a row (4 floats or 8 bfloat16) as floats; both addresses 16-byte aligned
+__device__ __forceinline__ void mc_load16(const float* src, float* dst) {
+    *reinterpret_cast<float4*>(dst) = *reinterpret_cast<const float4*>(src);
+}
+__device__ __forceinline__ void mc_load16(const __nv_bfloat16* src, float* dst) {
+    const uint4 raw = *reinterpret_cast<const uint4*>(src);
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+    const float2 f0 = __bfloat1622float2(h[0]), f1 = __bfloat1622float2(h[1]);
+    const float2 f2 = __bfloat1622float2(h[2]), f3 = __bfloat1622float2(h[3]);
+    reinterpret_cast<float4*>(dst)[0] = make_float4(f0.x, f0.y, f1.x, f1.y);
+    reinterpret_cast<float4*>(dst)[1] = make_float4(f2.x, f2.y, f3.x, f3.y);
+}
+
+// 4 or 8 floats as 16 bytes of a row
+__device__ __forceinline__ void mc_store16(float* dst, const float* v) {
+    *reinterpret_cast<float4*>(dst) = *reinterpret_cast<const float4*>(v);
+}
+__device__ __forceinline__ void mc_store16(__nv_bfloat16* dst, const float* v) {
+    uint4 raw;
+    __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&raw);
+    h[0] = __floats2bfloat162_rn(v[0], v[1]);
+    h[1] = __floats2bfloat162_rn(v[2], v[3]);
+    h[2] = __floats2bfloat162_rn(v[4], v[5]);
+    h[3] = __floats2bfloat162_rn(v[6], v[7]);
+    *reinterpret_cast<uint4*>(dst) = raw;
+}
+
 // ---------------------------------------------------------------------------
 // Short causal convolution per channel with bias and silu.  The filter's last tap is the current
 // token's; inputs before the run come from the sequence's state row (the last taps-1 inputs, oldest
@@ -613,6 +640,56 @@ conv_silu_kernel(ConvArgs a) {
         acc = fmaf(a.w[(size_t)c * a.taps + j], v, acc);
     }
     gl_store((TA*)a.out + (size_t)t * a.C + c, rc_silu(acc));
+}
+
+// The same with 16 bytes of channels a thread (4 or 8 of them): columns, pitch and offset are whole pieces, and
+// the thread's TAPS x channels weights are one run of memory that it fetches 16 bytes at a time.  The sums run in
+// the order of the kernel above.
+template <typename TA, int TAPS>
+__global__ void __launch_bounds__(256)
+conv_silu_wide_kernel(ConvArgs a) {
+    constexpr int VEC = 16 / (int)sizeof(TA);
+    gl_grid_launch_dependents();
+    gl_grid_wait();
+    const int CV = a.C / VEC;
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= (long long)a.T * CV) return;
+    const int t = (int)(i / CV), c0 = (int)(i - (long long)t * CV) * VEC;
+    const int b = a.tok_seq[t];
+    const int idx = t - a.seq_qstart[b];
+    constexpr int back = TAPS - 1;
+    const float* tail = a.state + (size_t)a.seq_slot[b] * a.state_stride + a.tail_off;
+    __align__(16) float acc[VEC], v[VEC], w[VEC * TAPS];
+#pragma unroll
+    for (int q = 0; q < VEC * TAPS / 4; ++q)
+        reinterpret_cast<float4*>(w)[q] = reinterpret_cast<const float4*>(a.w + (size_t)c0 * TAPS)[q];
+#pragma unroll
+    for (int k = 0; k < VEC; ++k) acc[k] = a.bias ? a.bias[c0 + k] : 0.f;
+#pragma unroll
+    for (int j = 0; j < TAPS; ++j) {
+        const int rel = idx - back + j;               // place in the run; negative: before it
+        if (rel >= 0) {
+            mc_load16((const TA*)a.x + (size_t)(t - back + j) * a.ld + a.x_off + c0, v);
+        } else {
+#pragma unroll
+            for (int k = 0; k < VEC; ++k) v[k] = tail[(size_t)(c0 + k) * back + rel + back];
+        }
+#pragma unroll
+        for (int k = 0; k < VEC; ++k) acc[k] = fmaf(w[k * TAPS + j], v[k], acc[k]);
+    }
+#pragma unroll
+    for (int k = 0; k < VEC; ++k) acc[k] = rc_silu(acc[k]);
+    mc_store16((TA*)a.out + (size_t)t * a.C + c0, acc);
+}
+
+template <typename TA>
+static int launch_conv_silu_wide(const ConvArgs& a, dim3 grid, cudaStream_t stream) {
+    switch (a.taps) {
+        case 1: return gl_launch(conv_silu_wide_kernel<TA, 1>, grid, dim3(256), 0, stream, 1, a);
+        case 2: return gl_launch(conv_silu_wide_kernel<TA, 2>, grid, dim3(256), 0, stream, 1, a);
+        case 3: return gl_launch(conv_silu_wide_kernel<TA, 3>, grid, dim3(256), 0, stream, 1, a);
+        default: return gl_launch(conv_silu_wide_kernel<TA, 4>, grid, dim3(256), 0, stream, 1, a);
+    }
 }
 
 template <typename TA>
@@ -667,13 +744,19 @@ GL_API int gl_conv_silu(const ConvArgs* args, int act_dtype, cudaStream_t stream
         if (act_dtype == GL_BF16) return gl_launch(conv_silu_step_kernel<__nv_bfloat16>, g2, dim3(256), 0, stream, 1, a);
         return GL_ERR_DTYPE;
     }
+    // rows of whole, aligned 16-byte pieces: a thread takes a piece of channels
+    const int vec = act_dtype == GL_F32 ? 4 : 8;
+    const bool wide = a.taps <= 4 && ((size_t)a.w & 15) == 0 && a.C % vec == 0 && a.ld % vec == 0 && a.x_off % vec == 0 && ((size_t)a.x & 15) == 0 && ((size_t)a.out & 15) == 0;
+    const dim3 gw((unsigned)((n / vec + 255) / 256));
     if (act_dtype == GL_F32) {
-        rc = gl_launch(conv_silu_kernel<float>, g1, dim3(256), 0, stream, 1, a);
+        rc = wide ? launch_conv_silu_wide<float>(a, gw, stream)
+                  : gl_launch(conv_silu_kernel<float>, g1, dim3(256), 0, stream, 1, a);
         if (rc == 0 && a.taps > 1) rc = gl_launch(conv_tail_kernel<float>, g2, dim3(256), 0, stream, 1, a);
         return rc;
     }
     if (act_dtype == GL_BF16) {
-        rc = gl_launch(conv_silu_kernel<__nv_bfloat16>, g1, dim3(256), 0, stream, 1, a);
+        rc = wide ? launch_conv_silu_wide<__nv_bfloat16>(a, gw, stream)
+                  : gl_launch(conv_silu_kernel<__nv_bfloat16>, g1, dim3(256), 0, stream, 1, a);
         if (rc == 0 && a.taps > 1) rc = gl_launch(conv_tail_kernel<__nv_bfloat16>, g2, dim3(256), 0, stream, 1, a);
         return rc;
     }
@@ -1010,19 +1093,6 @@ memory_chunk_decay_kernel(MemoryChunkArgs a) {
         else p *= l + (1.0f - l) * rc_sigmoid(gl_load((const TA*)a.proj + (size_t)(qstart + s) * a.ld + a.f_off + h * a.D + d));
     }
     a.chunk_decay[(((size_t)b * a.n_chunks + chunk) * a.H + h) * a.D + d] = p;
-}
-
-// 16 bytes of a row (4 floats or 8 bfloat16) as floats into shared memory; both addresses 16-byte aligned
-__device__ __forceinline__ void mc_load16(const float* src, float* dst) {
-    *reinterpret_cast<float4*>(dst) = *reinterpret_cast<const float4*>(src);
-}
-__device__ __forceinline__ void mc_load16(const __nv_bfloat16* src, float* dst) {
-    const uint4 raw = *reinterpret_cast<const uint4*>(src);
-    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
-    const float2 f0 = __bfloat1622float2(h[0]), f1 = __bfloat1622float2(h[1]);
-    const float2 f2 = __bfloat1622float2(h[2]), f3 = __bfloat1622float2(h[3]);
-    reinterpret_cast<float4*>(dst)[0] = make_float4(f0.x, f0.y, f1.x, f1.y);
-    reinterpret_cast<float4*>(dst)[1] = make_float4(f2.x, f2.y, f3.x, f3.y);
 }
 
 // two 32-bit multiply-adds in one instruction (the pair's halves are independent and rounded like fmaf's)
