@@ -1084,18 +1084,19 @@ def memory_scan(kind: int, proj: torch.Tensor, state: torch.Tensor, ctx, H: int,
     if kind == MEMORY_BOUNDED_FORGET:
         _need(lower, "lower", torch.float32, (H * D,))
     out = empty((T, H * V), torch.float32, proj.device)
+    gated, plain = kind == MEMORY_GATED, kind == MEMORY_DECAY
+    chunk_tokens = SCAN_CHUNK_TOKENS
+    if plain:
+        chunk_tokens = DECAY_CHUNK_TOKENS if ctx.max_qlen >= DECAY_LONG_RUN else DECAY_CHUNK_TOKENS_SHORT
+        # every (sequence, chunk) keeps a whole state: many long sequences take longer chunks
+        while (ctx.n_seqs * -(-ctx.max_qlen // chunk_tokens) * H * D * V * 4 > MEMORY_CHUNKS_MAX_BYTES
+               and chunk_tokens < 1024):
+            chunk_tokens *= 2
+    chunks = -(-ctx.max_qlen // chunk_tokens)
     if (USE_MEMORY_CHUNKS and kind in (MEMORY_GATED, MEMORY_BOUNDED_FORGET, MEMORY_DECAY) and D <= MEMORY_CHUNKS_MAX_ROWS
-            and ctx.max_qlen >= (DECAY_CHUNKED_FROM if kind == MEMORY_DECAY else SCAN_CHUNKED_FROM)):
+            and ctx.max_qlen >= (DECAY_CHUNKED_FROM if plain else SCAN_CHUNKED_FROM)
+            and (not plain or ctx.n_seqs * chunks <= 65535)):          # (the grid's third size)
         # a long run: chunks of tokens side by side, a lane a column (two walks and a carry between them)
-        gated, plain = kind == MEMORY_GATED, kind == MEMORY_DECAY
-        chunk_tokens = SCAN_CHUNK_TOKENS
-        if plain:
-            chunk_tokens = DECAY_CHUNK_TOKENS if ctx.max_qlen >= DECAY_LONG_RUN else DECAY_CHUNK_TOKENS_SHORT
-            # every (sequence, chunk) keeps a whole state: many long sequences take longer chunks
-            while (ctx.n_seqs * -(-ctx.max_qlen // chunk_tokens) * H * D * V * 4 > MEMORY_CHUNKS_MAX_BYTES
-                   and chunk_tokens < 1024):
-                chunk_tokens *= 2
-        chunks = -(-ctx.max_qlen // chunk_tokens)
         cols = V + (1 if gated else 0)
         chunk_state = empty((ctx.n_seqs, chunks, H, D, cols), torch.float32, proj.device)
         chunk_decay = empty((ctx.n_seqs, chunks, H, D), torch.float32, proj.device)
