@@ -26,6 +26,8 @@ _ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
 # no --use_fast_math: expf, erff and division stay exact
 _BASE_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "-shared",
                "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden"]
+# sources with hundreds of kernel instances: the device code is split and compiled on all cores
+_SOURCE_FLAGS: Dict[str, Tuple[str, ...]] = {"recurrent.cu": ("-split-compile", "0")}
 _lock = threading.Lock()
 _loaded: Dict[str, ctypes.CDLL] = {}
 
@@ -51,7 +53,7 @@ def _digest(source: str, defines: Tuple[str, ...]) -> str:
     for name in [source, *_headers()]:
         with open(os.path.join(_HERE, name), "rb") as f:
             h.update(name.encode() + b"\0" + f.read() + b"\0")
-    h.update(" ".join(_ARCH_FLAGS + _BASE_FLAGS + list(defines)).encode())
+    h.update(" ".join(_ARCH_FLAGS + _BASE_FLAGS + list(_SOURCE_FLAGS.get(source, ())) + list(defines)).encode())
     return h.hexdigest()[:16]
 
 
@@ -92,7 +94,7 @@ def library_path(source: str, defines: Tuple[str, ...] = (), build: bool = True,
             continue
         so, stamp = os.path.join(d, name + ".so"), os.path.join(d, name + ".hash")
         tmp = os.path.join(d, f"{name}.{os.getpid()}_{threading.get_ident()}.tmp.so")
-        cmd = [_nvcc(), *_ARCH_FLAGS, *_BASE_FLAGS, *[f"-D{x}" for x in defines],
+        cmd = [_nvcc(), *_ARCH_FLAGS, *_BASE_FLAGS, *_SOURCE_FLAGS.get(source, ()), *[f"-D{x}" for x in defines],
                "-I", _HERE, "-o", tmp, os.path.join(_HERE, source)]
         if verbose:
             print(f"[gopherllm_b200] compiling {source}{' ' + ' '.join(defines) if defines else ''} "
