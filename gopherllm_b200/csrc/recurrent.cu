@@ -1190,7 +1190,7 @@ memory_chunk_walk_kernel(MemoryChunkArgs a) {
                 }
             }
         } else {
-    #pragma unroll 4
+#pragma unroll 4
             for (int e = threadIdx.x; e < ns * D; e += NT) {
                 const int s = e / D, d = e - s * D;
                 const size_t t = (size_t)(qstart + s0 + s);

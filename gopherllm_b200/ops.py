@@ -1045,7 +1045,9 @@ def memory_scan(kind: int, proj: torch.Tensor, state: torch.Tensor, ctx, H: int,
     MEMORY_DECAY: S <- keep S + take k v^T, o = S^T q + skip[h] v, with q and k of ``kv_heads`` heads (0: one per
     head), rotated first where ``cos`` and ``sin`` [T, half] are given (dim i of a head with dim i + half), then
     times q_scale and k_scale.  Either ``decay`` [H] (keep = decay[h], take = 1) or ``gates`` with ``a_log`` and
-    ``dt_bias`` [H]: dt = softplus(gates[t, f_off + h] + dt_bias[h]), keep = exp(-exp(a_log[h]) dt), take = dt."""
+    ``dt_bias`` [H]: dt = softplus(gates[t, f_off + h] + dt_bias[h]), keep = exp(-exp(a_log[h]) dt), take = dt.
+    Long runs of the gated, the bounded-forget and the plain-decay kind (heads of up to MEMORY_CHUNKS_MAX_ROWS rows)
+    are walked as chunks side by side; which form runs depends on the step's longest run alone."""
     _need(proj, "proj")
     rot_half = 0
     if kind == MEMORY_DECAY:
