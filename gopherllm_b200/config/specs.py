@@ -27,7 +27,7 @@ class NormSpec:
     dim: int
     eps: float
     bias: bool = True
-    # the stored weight is the distance from this value (1.0: a weight stored around zero, applied as 1 + w)
+    # the file holds the weight minus this value (1.0: the norm multiplies by 1 + w)
     weight_offset: float = 0.0
 
 

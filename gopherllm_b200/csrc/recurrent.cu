@@ -522,7 +522,7 @@ GL_API int gl_memory_scan(const MemoryScanArgs* args, int act_dtype, cudaStream_
 //   out[t, h, j] = o[t, h, j] / sqrt(mean_j o[t, h, :]^2 + eps) * w * sigmoid(gate[t, h*V + j])
 // w is [H*V] (w_per_head = 1) or [V] shared by the heads (null: no weight); gate (activation type, row pitch
 // gate_ld, first column gate_off) may be absent; gate_silu multiplies by silu(gate) instead of the sigmoid.
-// gate_first: the gate comes before the norm, out = g / sqrt(mean_j g^2 + eps) * w with g = o * act(gate).
+// gate_first: gating first, then the norm of the gated values: out = g / sqrt(mean_j g^2 + eps) * w with g = o * act(gate).
 // One warp per (token, head).
 // ---------------------------------------------------------------------------
 template <typename TA>
