@@ -34,7 +34,7 @@ RELEASED = -1        # in a sequence's list of pages: this one lay before the wi
 @dataclass
 class KVView:
     """What a mixer gets for its run: this entry's pages of keys and values
-    ([pages, kv_heads, PAGE, head_dim] and [pages, kv_heads, PAGE, value_dim]), the group whose page table
+    ([pages, kv_heads, PAGE, head_dim] and [pages, value_heads, PAGE, value_dim]), the group whose page table
     (ctx.pages[group]) addresses them, and whether this run writes them."""
     group: int
     k: torch.Tensor
@@ -112,7 +112,8 @@ class SequenceCache:
                 r = g.req
                 g.keys = torch.empty((len(g.entries), self.n_pages, r.num_kv_heads, PAGE, r.head_dim),
                                      dtype=dtype, device=device)
-                g.values = torch.empty((len(g.entries), self.n_pages, r.num_kv_heads, PAGE, r.value_dim or r.head_dim),
+                g.values = torch.empty((len(g.entries), self.n_pages, r.value_heads or r.num_kv_heads, PAGE,
+                                        r.value_dim or r.head_dim),
                                        dtype=dtype, device=device)
         # per-slot bookkeeping
         self._length = [0] * self.max_slots
@@ -128,7 +129,8 @@ class SequenceCache:
     def bytes_per_position(self) -> int:
         """Key and value bytes one cached position occupies, all entries together."""
         es = torch.empty((), dtype=self.dtype).element_size()
-        return sum(len(g.entries) * g.req.num_kv_heads * (g.req.head_dim + (g.req.value_dim or g.req.head_dim)) * es
+        return sum(len(g.entries) * (g.req.num_kv_heads * g.req.head_dim
+                                     + (g.req.value_heads or g.req.num_kv_heads) * (g.req.value_dim or g.req.head_dim)) * es
                    for g in self.groups)
 
     # -- views ------------------------------------------------------------

@@ -16,6 +16,8 @@ from . import gozolix as _gozolix  # registers the architecture
 from .gozolix import GozolixConfig
 from . import lilupel as _lilupel  # registers the architecture
 from .lilupel import LilupelConfig
+from . import darusun as _darusun  # registers the architecture
+from .darusun import DarusunConfig
 
 
 def read_config_json(folder: str) -> dict:

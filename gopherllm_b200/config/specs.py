@@ -29,6 +29,8 @@ class NormSpec:
     bias: bool = True
     # the file holds the weight minus this value (1.0: the norm multiplies by 1 + w)
     weight_offset: float = 0.0
+    # the weight is a single number for all coordinates (the file holds a tensor without axes)
+    single_weight: bool = False
 
 
 @dataclass(frozen=True)

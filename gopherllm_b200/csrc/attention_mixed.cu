@@ -21,7 +21,7 @@ struct MixedAttnArgs {
     float* pairs;             // [T, nH, nVal, vd] 32-bit; nVal = nKV with a table, 1 without
     void* out;                // [T, nH*vd] activation type
     const void* k_cache;      // [pages, nKV, GL_PAGE, hd] cache type
-    const void* v_cache;      // [pages, nKV, GL_PAGE, vd] cache type
+    const void* v_cache;      // [pages, nKV (nVH), GL_PAGE, vd] cache type
     const float* mix;         // [nH, nH] or null
     const int* seq_qstart;
     const int* seq_qlen;
@@ -37,7 +37,11 @@ struct MixedAttnArgs {
     float softcap;            // > 0: scores are capped smoothly at +-softcap
     const float* slopes;      // [nH] or null: head h's penalty per position of distance
     const float* sinks;       // [nH] or null: e^(sinks[h]) joins the softmax's denominator of head h (no key, no value)
+    int nVH;                  // heads of the value cache where they are more than the key heads (a multiple of nKV; 0: nKV):
+                              // without a table, query head g then takes the values of head g / (nH / nVH)
 };
+
+__host__ __device__ __forceinline__ int am_value_heads(const MixedAttnArgs& a) { return a.nVH > 0 ? a.nVH : a.nKV; }
 
 // What a sink does to a finished softmax with maximum m and sum l (of e^(s - m)): the factor on the weighted
 // values' sum, 1 / (l + e^(sink - m)), taken against the larger of m and the sink so that nothing overflows.
@@ -74,7 +78,8 @@ attn_pairs_kernel(MixedAttnArgs a) {
     const int nVal = a.mix ? a.nKV : 1;
     const int g = blockIdx.y / nVal;                              // query head
     const int kh = g / (a.nH / a.nKV);                            // its key head
-    const int vh = a.mix ? blockIdx.y - g * nVal : kh;            // the pair's value head
+    const int nvh = am_value_heads(a);
+    const int vh = a.mix ? blockIdx.y - g * nVal : g / (a.nH / nvh);      // the pair's value head
     const int qlen = a.seq_qlen[b];
     const int row0 = blockIdx.x * AM_ROWS;
     if (row0 >= qlen) return;
@@ -103,7 +108,7 @@ attn_pairs_kernel(MixedAttnArgs a) {
     for (int page_i = lo_cta / GL_PAGE; page_i <= p_last / GL_PAGE; ++page_i) {
         const int page = gl_checked(pg[gl_checked(page_i, a.max_pages, GL_BAD_POSITION)], a.n_pages > 0 ? a.n_pages : 0x7fffffff, GL_BAD_PAGE);
         const TC* kp = (const TC*)a.k_cache + ((size_t)page * a.nKV + kh) * GL_PAGE * hd;
-        const TC* vp = (const TC*)a.v_cache + ((size_t)page * a.nKV + vh) * GL_PAGE * vd;
+        const TC* vp = (const TC*)a.v_cache + ((size_t)page * nvh + vh) * GL_PAGE * vd;
         const int j0 = page_i * GL_PAGE;
         __syncthreads();
         for (int e = threadIdx.x; e < GL_PAGE * hd; e += blockDim.x) {
@@ -173,7 +178,8 @@ attn_pairs_decode_kernel(MixedAttnArgs a) {
     const int nVal = a.mix ? a.nKV : 1;
     const int g = blockIdx.x / nVal;
     const int kh = g / (a.nH / a.nKV);
-    const int vh = a.mix ? blockIdx.x - g * nVal : kh;
+    const int nvh = am_value_heads(a);
+    const int vh = a.mix ? blockIdx.x - g * nVal : g / (a.nH / nvh);
     const int p = a.seq_ctx[b];                         // the token's position; keys lo..p
     const int lo = (a.window > 0 && p - a.window + 1 > 0) ? p - a.window + 1 : 0;
     const int row = a.seq_qstart[b];
@@ -189,7 +195,7 @@ attn_pairs_decode_kernel(MixedAttnArgs a) {
     for (int page_i = lo / GL_PAGE + warp; page_i <= p / GL_PAGE; page_i += AM_DWARPS) {
         const int page = gl_checked(pg[gl_checked(page_i, a.max_pages, GL_BAD_POSITION)], a.n_pages > 0 ? a.n_pages : 0x7fffffff, GL_BAD_PAGE);
         const TC* kp = (const TC*)a.k_cache + ((size_t)page * a.nKV + kh) * GL_PAGE * hd;
-        const TC* vp = (const TC*)a.v_cache + ((size_t)page * a.nKV + vh) * GL_PAGE * vd;
+        const TC* vp = (const TC*)a.v_cache + ((size_t)page * nvh + vh) * GL_PAGE * vd;
         const int j0 = page_i * GL_PAGE;
 #pragma unroll 1
         for (int half = 0; half < GL_PAGE / 32; ++half) {
@@ -302,8 +308,13 @@ attn_group_decode_kernel(MixedAttnArgs a) {
     const int page_last = min(p / GL_PAGE, page_first + a.pages_per_split - 1);      // may lie before page_first: nothing to do
     const TA* qsrc = (const TA*)a.q + ((size_t)row * a.nH + (size_t)kh * gq) * hd;
     for (int i = threadIdx.x; i < gq * hd; i += AM_GTHREADS) qv[i] = gl_load(qsrc + i);
-    const int vh = a.mix ? warp : kh;                   // this warp's value head
-    const bool has_values = a.mix ? warp < a.nKV : warp == 0;
+    // this warp's value head: with a table every value head meets every query head; without one the key head's
+    // query heads fall into as many equal runs as it has value heads, a warp a run
+    const int nvh = am_value_heads(a);
+    const int runs = a.mix ? 1 : nvh / a.nKV;           // value heads of this key head
+    const int per = gq / runs;                          // query heads that share one of them
+    const int vh = a.mix ? warp : kh * runs + warp;
+    const bool has_values = a.mix ? warp < a.nKV : warp < runs;
     float acc[GQ][NACC];
 #pragma unroll
     for (int g = 0; g < GQ; ++g)
@@ -337,7 +348,7 @@ attn_group_decode_kernel(MixedAttnArgs a) {
         }
         __syncthreads();
         if (has_values) {
-            const TC* vp = (const TC*)a.v_cache + ((size_t)page * a.nKV + vh) * GL_PAGE * vd;
+            const TC* vp = (const TC*)a.v_cache + ((size_t)page * nvh + vh) * GL_PAGE * vd;
 #pragma unroll
             for (int g = 0; g < GQ; ++g) {
                 if (g < gq) {
@@ -366,7 +377,7 @@ attn_group_decode_kernel(MixedAttnArgs a) {
                 for (int kk = 0; kk < KB; ++kk) {
 #pragma unroll
                     for (int g = 0; g < GQ; ++g) {
-                        if (g < gq) {
+                        if (g < gq && (a.mix || g / per == warp)) {
                             const float pk = sc[g * GL_PAGE + k0 + kk];
 #pragma unroll
                             for (int i = 0; i < NACC; ++i) acc[g][i] = fmaf(pk, v[kk][i], acc[g][i]);
@@ -385,7 +396,7 @@ attn_group_decode_kernel(MixedAttnArgs a) {
     if (has_values) {
 #pragma unroll
         for (int g = 0; g < GQ; ++g) {
-            if (g < gq) {
+            if (g < gq && (a.mix || g / per == warp)) {
                 float* o = a.parts + ((((size_t)b * a.nH + (size_t)kh * gq + g) * nVal + (a.mix ? vh : 0)) * a.splits + split) * vd;
 #pragma unroll
                 for (int i = 0; i < NACC; ++i) {
@@ -475,7 +486,8 @@ template <typename TA, typename TC, int NACC>
 static int launch_mixed(const MixedAttnArgs& a, cudaStream_t stream) {
     const int pairs = a.nH * (a.mix ? a.nKV : 1);
     int rc;
-    if (a.max_qlen == 1 && a.nH / a.nKV <= 8 && a.nKV <= AM_GTHREADS / 32 && NACC <= 4 && a.parts && a.ml && a.splits > 0) {
+    if (a.max_qlen == 1 && a.nH / a.nKV <= 8 && (a.mix ? a.nKV : am_value_heads(a) / a.nKV) <= AM_GTHREADS / 32 && NACC <= 4 &&
+        a.parts && a.ml && a.splits > 0) {
         rc = launch_group_decode<TA, TC, NACC>(a, stream);
         if (rc != 0) return rc;
         return gl_launch(head_mix_split_kernel<TA>, dim3(a.nH, a.B), dim3(a.vd <= 64 ? 64 : 128), (size_t)(a.mix ? a.nH : 1) * a.splits * sizeof(float), stream, 1, a);
@@ -527,7 +539,8 @@ static int dispatch_mixed(const MixedAttnArgs& a, cudaStream_t stream) {
 GL_API int gl_attention_mixed(const MixedAttnArgs* args, int act_dtype, int cache_dtype, cudaStream_t stream) {
     const MixedAttnArgs& a = *args;
     if (a.B <= 0 || a.max_qlen <= 0 || a.T <= 0) return GL_OK;
-    if (a.hd <= 0 || a.hd > 256 || a.vd <= 0 || a.vd > 256 || a.nH <= 0 || a.nKV <= 0 || a.nH % a.nKV) return GL_ERR_SHAPE;
+    if (a.hd <= 0 || a.hd > 512 || a.vd <= 0 || a.vd > 256 || a.nH <= 0 || a.nKV <= 0 || a.nH % a.nKV) return GL_ERR_SHAPE;
+    if (a.nVH < 0 || (a.nVH > 0 && (a.nVH % a.nKV || a.nH % a.nVH || (a.mix && a.nVH != a.nKV)))) return GL_ERR_SHAPE;
     if (a.B > 65535 || a.nH * a.nKV > 65535) return GL_ERR_SHAPE;
     if (act_dtype == GL_F32 && cache_dtype == GL_F32) return dispatch_mixed<float, float>(a, stream);
     if (act_dtype == GL_BF16 && cache_dtype == GL_BF16) return dispatch_mixed<__nv_bfloat16, __nv_bfloat16>(a, stream);

@@ -46,6 +46,8 @@ struct PairsArgs {
     void* out;                // [T, nH*vd] bf16 or null: without a mixing table (nVal 1) the result goes here, rounded,
                               // and no second kernel has to read the 32-bit pairs again
     const float* sinks;       // [nH] or null: e^(sinks[h]) joins the softmax's denominator of head h
+    int nVH;                  // heads of the value cache where they are more than the key heads (0: nKV); without a
+                              // table, query head h then takes the values of head h / (nH / nVH)
 };
 
 __device__ __forceinline__ unsigned ap_smem(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
@@ -103,7 +105,8 @@ attn_pairs_tc_kernel(PairsArgs a) {
     const int b = blockIdx.z;
     const int h = blockIdx.y / a.nVal;                         // query head
     const int g = h / (a.nH / a.nKV);                          // its key head
-    const int vh = a.nVal > 1 ? blockIdx.y - h * a.nVal : g;   // the pair's value head
+    const int nvh = a.nVH > 0 ? a.nVH : a.nKV;
+    const int vh = a.nVal > 1 ? blockIdx.y - h * a.nVal : h / (a.nH / nvh);   // the pair's value head
     const int qlen = a.seq_qlen[b];
     const int n_qtiles = (qlen + AP_BM - 1) / AP_BM;
     const int qt = n_qtiles - 1 - (int)blockIdx.x;           // longest rows first
@@ -120,7 +123,7 @@ attn_pairs_tc_kernel(PairsArgs a) {
     const __nv_bfloat16* K = (const __nv_bfloat16*)a.k_cache;
     const __nv_bfloat16* V = (const __nv_bfloat16*)a.v_cache;
     const size_t head_off = (size_t)g * GL_PAGE * AP_HD, page_stride = (size_t)a.nKV * GL_PAGE * AP_HD;
-    const size_t vhead_off = (size_t)vh * GL_PAGE * AP_VD, vpage_stride = (size_t)a.nKV * GL_PAGE * AP_VD;
+    const size_t vhead_off = (size_t)vh * GL_PAGE * AP_VD, vpage_stride = (size_t)nvh * GL_PAGE * AP_VD;
     const int total = ctx + qlen;
 
     // the query tile, then the first page
@@ -317,6 +320,7 @@ GL_API int gl_attention_pairs_tc(const PairsArgs* args, cudaStream_t stream) {
     const PairsArgs& a = *args;
     if (a.B <= 0 || a.max_qlen <= 0) return GL_OK;
     if (a.nH <= 0 || a.nKV <= 0 || a.nH % a.nKV || (a.nVal != 1 && a.nVal != a.nKV)) return GL_ERR_SHAPE;
+    if (a.nVH < 0 || (a.nVH > 0 && (a.nH % a.nVH || (a.nVal != 1 && a.nVH != a.nKV)))) return GL_ERR_SHAPE;
     if (a.B > 65535 || a.nH * a.nVal > 65535) return GL_ERR_SHAPE;
     const size_t smem = 3 * (size_t)AP_TILE + 2 * (size_t)AP_VTILE;
     static bool configured = false;

@@ -32,7 +32,16 @@ struct RouteArgs {
     float* weights;           // [T, top]
     int T, E, top, groups, keep;
     float scale;
+    const float* bias;        // [E] or null: added to the logits
+    int softmax_chosen;       // 1: the largest LOGITS are chosen and weighted by the softmax over the chosen logits alone
+                              // (times scale; one group); 0: sigmoid scores as above
 };
+
+// a token's score for expert e from its logit
+__device__ __forceinline__ float moe_score(const RouteArgs& a, float z, int e) {
+    if (a.bias) z += a.bias[e];
+    return a.softmax_chosen ? z : 1.0f / (1.0f + expf(-z));
+}
 
 // the largest value among sc[e], e = first + lane, first + lane + 32, ... < last, and its (lowest) index
 __device__ __forceinline__ void moe_argmax(const float* sc, int first, int last, int lane, float& best, int& at) {
@@ -83,6 +92,27 @@ __device__ __forceinline__ void moe_choose(const RouteArgs& a, float* sc, float*
             if (gsc[e / per] != -INFINITY) sc[e] = -1.0f;    // scores lie in (0, 1): -1 is never chosen before them
         __syncwarp();
     }
+    if (a.softmax_chosen) {
+        float first = 0.f, sum = 0.f;
+        for (int k = 0; k < a.top; ++k) {
+            float b;
+            int e;
+            moe_argmax(sc, 0, a.E, lane, b, e);
+            if (k == 0) first = b;                           // the largest: the softmax is taken against it
+            const float w = expf(b - first);
+            sum += w;
+            __syncwarp();
+            if (lane == 0) {
+                a.ids[(size_t)t * a.top + k] = e;
+                a.weights[(size_t)t * a.top + k] = w;
+                sc[e] = -INFINITY;
+            }
+            __syncwarp();
+        }
+        const float f = a.scale / sum;
+        for (int k = lane; k < a.top; k += 32) a.weights[(size_t)t * a.top + k] *= f;
+        return;
+    }
     float sum = 0.f;
     for (int k = 0; k < a.top; ++k) {
         float b;
@@ -112,7 +142,7 @@ moe_route_kernel(RouteArgs a) {
     if (t >= a.T) return;
     float* sc = smem + (size_t)warp * (a.E + a.groups);      // [E] scores, then [groups] group scores
     float* gsc = sc + a.E;
-    for (int e = lane; e < a.E; e += 32) sc[e] = 1.0f / (1.0f + expf(-a.logits[(size_t)t * a.E + e]));
+    for (int e = lane; e < a.E; e += 32) sc[e] = moe_score(a, a.logits[(size_t)t * a.E + e], e);
     __syncwarp();
     moe_choose(a, sc, gsc, t, lane);
 }
@@ -147,7 +177,7 @@ moe_route_from_kernel(RouteFromArgs f) {
         float z = 0.f;
         for (int k = lane; k < f.K; k += 32) z = fmaf(xs[k], w[k], z);
         z = gl_warp_sum(z);
-        if (lane == 0) sc[e] = 1.0f / (1.0f + expf(-z));
+        if (lane == 0) sc[e] = moe_score(a, z, e);
     }
     __syncthreads();
     if (warp == 0) moe_choose(a, sc, gsc, t, lane);
@@ -158,7 +188,7 @@ GL_API int gl_moe_route_from(const RouteFromArgs* args, int x_dtype, cudaStream_
     const RouteArgs& a = f.r;
     if (a.T <= 0) return GL_OK;
     if (f.K <= 0 || a.E <= 0 || a.top <= 0 || a.top > a.E || a.groups <= 0 || a.E % a.groups || a.keep <= 0 || a.keep > a.groups) return GL_ERR_SHAPE;
-    if ((long long)a.keep * (a.E / a.groups) < a.top) return GL_ERR_SHAPE;
+    if ((long long)a.keep * (a.E / a.groups) < a.top || (a.softmax_chosen && a.groups != 1)) return GL_ERR_SHAPE;
     const size_t smem = (size_t)(a.E + a.groups + f.K) * sizeof(float);
     if (smem > 48 * 1024) return GL_ERR_SMEM;
     int rc;
@@ -172,7 +202,7 @@ GL_API int gl_moe_route(const RouteArgs* args, cudaStream_t stream) {
     const RouteArgs& a = *args;
     if (a.T <= 0) return GL_OK;
     if (a.E <= 0 || a.top <= 0 || a.top > a.E || a.groups <= 0 || a.E % a.groups || a.keep <= 0 || a.keep > a.groups) return GL_ERR_SHAPE;
-    if ((long long)a.keep * (a.E / a.groups) < a.top) return GL_ERR_SHAPE;
+    if ((long long)a.keep * (a.E / a.groups) < a.top || (a.softmax_chosen && a.groups != 1)) return GL_ERR_SHAPE;
     const size_t smem = 4 * (size_t)(a.E + a.groups) * sizeof(float);
     if (smem > 48 * 1024) return GL_ERR_SMEM;
     return gl_launch(moe_route_kernel, dim3((a.T + 3) / 4), dim3(128), smem, stream, 1, a) == 0 ? GL_OK : GL_ERR_LAUNCH;

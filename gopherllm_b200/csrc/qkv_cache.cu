@@ -258,6 +258,13 @@ struct QkvRowNormArgs {
     int q_only;                    // the rows hold queries alone; nothing is written to the cache
     int head_unit;                 // after the rotation every head of q and k is divided by its own root mean square
                                    // over hd (eps inside the root, no weight)
+    const float* talk;             // [nH, nH] or null: a table that mixes the heads' SCORES before the softmax,
+                                   // s'_h = sum_g talk[h, g] (q_g . k_c(g)).  The sum is taken on the queries: q_out
+                                   // is then [T, nH, nKV*hd], head h holding, for every key head c, the sum of
+                                   // talk[h, g] q_g over the query heads g of c, so that s'_h is ONE product of
+                                   // that row with the position's key heads side by side
+    int k_joined;                  // the key cache holds a position's heads side by side as one row:
+                                   // [pages, 1, GL_PAGE, nKV*hd]
 };
 
 template <typename TA, typename TC>
@@ -327,18 +334,30 @@ qkv_rownorm_cache_kernel(QkvRowNormArgs a) {
         }
         __syncthreads();
     }
-    TA* qo = (TA*)a.q_out + (size_t)t * nq;
     const int pos = a.tok_pos[t];
     float q_mul = a.q_scale;
     if (a.temp_every > 0.f)
         q_mul *= 1.0f + a.temp_coef * logf((float)floor((double)(pos + 1) / (double)a.temp_every) + 1.0f);
-    for (int i = threadIdx.x; i < nq; i += blockDim.x) gl_store(qo + i, v[i] * q_mul);
+    if (a.talk) {
+        const int wide = a.nKV * a.hd, per = a.nH / a.nKV;
+        TA* qo = (TA*)a.q_out + (size_t)t * a.nH * wide;
+        for (int i = threadIdx.x; i < a.nH * wide; i += blockDim.x) {
+            const int h = i / wide, r = i - h * wide, c = r / a.hd, d = r - c * a.hd;
+            float y = 0.f;
+            for (int g = c * per; g < (c + 1) * per; ++g) y = fmaf(a.talk[h * a.nH + g], v[(size_t)g * a.hd + d], y);
+            gl_store(qo + i, y * q_mul);
+        }
+    } else {
+        TA* qo = (TA*)a.q_out + (size_t)t * nq;
+        for (int i = threadIdx.x; i < nq; i += blockDim.x) gl_store(qo + i, v[i] * q_mul);
+    }
     if (!a.write_kv || a.q_only) return;
     const int slot = gl_checked(pos / GL_PAGE, a.max_pages, GL_BAD_POSITION);
     const int page = gl_checked(a.pages[(size_t)a.tok_seq[t] * a.max_pages + slot], a.n_pages > 0 ? a.n_pages : 0x7fffffff, GL_BAD_PAGE);
     for (int i = threadIdx.x; i < nk; i += blockDim.x) {
         const int head = i / a.hd, d = i - head * a.hd;
-        gl_store((TC*)a.k_cache + (((size_t)page * a.nKV + head) * GL_PAGE + (pos % GL_PAGE)) * a.hd + d, v[nq + i]);
+        if (a.k_joined) gl_store((TC*)a.k_cache + ((size_t)page * GL_PAGE + (pos % GL_PAGE)) * nk + i, v[nq + i]);
+        else gl_store((TC*)a.k_cache + (((size_t)page * a.nKV + head) * GL_PAGE + (pos % GL_PAGE)) * a.hd + d, v[nq + i]);
     }
     for (int i = threadIdx.x; i < nv; i += blockDim.x) {
         const int head = i / a.vd, d = i - head * a.vd;

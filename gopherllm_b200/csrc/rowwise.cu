@@ -428,6 +428,67 @@ GL_API int gl_gated_act(const void* gu, void* out, int T, int F, int act, int ac
     return GL_ERR_DTYPE;
 }
 
+// The same between the products of a gated feed-forward whose first product carries more columns: rows of ld
+// columns, the gate's F from column 0 and the up projection's F behind them; with row_gate >= 0 column
+// row_gate holds one more number a row, and the row's result is multiplied by its sigmoid (a feed-forward that is
+// added with a learned share per token: the share is applied before the last product, which is linear).
+template <typename TA>
+__global__ void __launch_bounds__(256)
+gated_act_rows_kernel(const TA* gu, TA* __restrict__ out, long long n, int F, int ld, int row_gate, int act) {
+    gl_grid_launch_dependents();
+    gl_grid_wait();
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+        const long long t = i / F;
+        const int j = (int)(i - t * F);
+        const TA* row = gu + (size_t)t * ld;
+        const float g = gl_load(row + j), u = gl_load(row + F + j);
+        float y = gl_activate<true>(g, act) * u;
+        if (row_gate >= 0) y *= 1.0f / (1.0f + expf(-gl_load(row + row_gate)));
+        gl_store(out + i, y);
+    }
+}
+
+GL_API int gl_gated_act_rows(const void* gu, void* out, int T, int F, int ld, int row_gate, int act, int act_dtype,
+                             cudaStream_t stream) {
+    if (T <= 0) return GL_OK;
+    if (F <= 0 || ld < 2 * F || row_gate >= ld) return GL_ERR_SHAPE;
+    const long long n = (long long)T * F;
+    const long long want = (n + 255) / 256;
+    const dim3 grid((unsigned)(want > 8192 ? 8192 : want));
+    if (act_dtype == GL_F32)
+        return gl_launch(gated_act_rows_kernel<float>, grid, dim3(256), 0, stream, 1, (const float*)gu, (float*)out, n, F, ld,
+                         row_gate, act);
+    if (act_dtype == GL_BF16)
+        return gl_launch(gated_act_rows_kernel<__nv_bfloat16>, grid, dim3(256), 0, stream, 1, (const __nv_bfloat16*)gu,
+                         (__nv_bfloat16*)out, n, F, ld, row_gate, act);
+    return GL_ERR_DTYPE;
+}
+
+// ---------------------------------------------------------------------------
+// An activation with two learned numbers, in place: above zero the parabola up * z^2 + z / 2, at and below zero
+// down * (e^z - 1 - z) + z / 2 (the same slope on both sides of zero).  32-bit arithmetic, one rounding.
+// ---------------------------------------------------------------------------
+template <typename TA>
+__global__ void __launch_bounds__(256)
+xielu_kernel(TA* x, long long n, float up, float down) {
+    gl_grid_launch_dependents();
+    gl_grid_wait();
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+        const float z = gl_load(x + i);
+        const float y = z > 0.f ? fmaf(up * z, z, 0.5f * z) : fmaf(down, expm1f(z) - z, 0.5f * z);
+        gl_store(x + i, y);
+    }
+}
+
+GL_API int gl_xielu(void* x, long long n, float up, float down, int act_dtype, cudaStream_t stream) {
+    if (n <= 0) return GL_OK;
+    const long long want = (n + 255) / 256;
+    const dim3 grid((unsigned)(want > 8192 ? 8192 : want));
+    if (act_dtype == GL_F32) return gl_launch(xielu_kernel<float>, grid, dim3(256), 0, stream, 1, (float*)x, n, up, down);
+    if (act_dtype == GL_BF16) return gl_launch(xielu_kernel<__nv_bfloat16>, grid, dim3(256), 0, stream, 1, (__nv_bfloat16*)x, n, up, down);
+    return GL_ERR_DTYPE;
+}
+
 // ---------------------------------------------------------------------------
 // Entering a pass of a looped range of layers: x[t, :] += base[t, :] + table[row, :]
 // (base, the stream as it left the embedding, may be absent; table: one learned vector per pass).

@@ -1247,7 +1247,8 @@ class _QkvRowNormArgs(Structure):
                 ("T", c_int), ("ld", c_int), ("nH", c_int), ("nKV", c_int), ("hd", c_int), ("vd", c_int),
                 ("half", c_int), ("max_pages", c_int), ("interleaved", c_int), ("write_kv", c_int),
                 ("eps", c_float), ("q_scale", c_float), ("n_pages", c_int),
-                ("temp_coef", c_float), ("temp_every", c_float), ("q_only", c_int), ("head_unit", c_int)]
+                ("temp_coef", c_float), ("temp_every", c_float), ("q_only", c_int), ("head_unit", c_int),
+                ("talk", c_void_p), ("k_joined", c_int)]
 
 
 def qkv_rownorm_to_cache(qkv: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, ctx, pages: torch.Tensor,
@@ -1255,14 +1256,19 @@ def qkv_rownorm_to_cache(qkv: torch.Tensor, k_cache: torch.Tensor, v_cache: torc
                          cos: Optional[torch.Tensor], sin: Optional[torch.Tensor], interleaved: bool,
                          q_gamma: Optional[torch.Tensor], k_gamma: Optional[torch.Tensor], eps: float,
                          write_kv: bool = True, q_temp: Optional[tuple] = None, q_only: bool = False,
-                         head_unit: bool = False) -> torch.Tensor:
+                         head_unit: bool = False, talk: Optional[torch.Tensor] = None,
+                         k_joined: bool = False) -> torch.Tensor:
     """Queries and keys normalised over the whole projection (root mean square, weights [nH*hd] and
     [nKV*hd]; None: no norm), rotated and scaled; keys and values written to the tokens' cache rows.
     ``head_unit``: after the rotation every head of q and k is divided by its own root mean square (eps
     inside the root, no weight).
     qkv [T, ld]: q, k, v side by side from column 0 (``q_only``: queries alone, nothing is written).
     ``q_temp`` = (coef, every): q also times 1 + coef * ln(floor((position + 1) / every) + 1).
-    Returns q [T, nH*hd]."""
+    ``talk`` [nH, nH] float32: a table that mixes the heads' scores before the softmax, s'_h = sum_g talk[h, g] s_g,
+    taken on the queries: the result is [T, nH, nKV*hd], head h holding for every key head c the sum of
+    talk[h, g] q_g over c's query heads g, so that s'_h is one product with the position's key heads side by side.
+    ``k_joined``: the key cache holds them so, [pages, 1, PAGE, nKV*hd].
+    Returns q [T, nH*hd] (with ``talk``: [T, nH*nKV*hd])."""
     _need(qkv, "qkv")
     T, ld = qkv.shape
     nq, nk, nv = num_heads * head_dim, num_kv_heads * head_dim, num_kv_heads * value_dim
@@ -1274,7 +1280,10 @@ def qkv_rownorm_to_cache(qkv: torch.Tensor, k_cache: torch.Tensor, v_cache: torc
         raise KernelError("qkv_rownorm_to_cache: the query temperature's period must be positive")
     if ld < nq + nk + nv:
         raise KernelError("qkv_rownorm_to_cache: the projection's rows are too short")
-    if tuple(k_cache.shape[1:]) != (num_kv_heads, PAGE, head_dim) or tuple(v_cache.shape[1:]) != (num_kv_heads, PAGE, value_dim):
+    k_shape = (1, PAGE, num_kv_heads * head_dim) if k_joined else (num_kv_heads, PAGE, head_dim)
+    if talk is not None:
+        _need(talk, "talk", torch.float32, (num_heads, num_heads))
+    if tuple(k_cache.shape[1:]) != k_shape or tuple(v_cache.shape[1:]) != (num_kv_heads, PAGE, value_dim):
         raise KernelError(f"cache pages do not fit: keys {tuple(k_cache.shape)}, values {tuple(v_cache.shape)}")
     half = 0
     if cos is not None:
@@ -1285,13 +1294,13 @@ def qkv_rownorm_to_cache(qkv: torch.Tensor, k_cache: torch.Tensor, v_cache: torc
         _need(q_gamma, "q_gamma", torch.float32, (nq,))
     if k_gamma is not None:
         _need(k_gamma, "k_gamma", torch.float32, (nk,))
-    q = empty((T, nq), qkv.dtype, qkv.device)
+    q = empty((T, nq * num_kv_heads if talk is not None else nq), qkv.dtype, qkv.device)
     a = _QkvRowNormArgs(qkv.data_ptr(), q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), _addr(cos), _addr(sin),
                         _addr(q_gamma), _addr(k_gamma), ctx.tok_seq.data_ptr(), ctx.tok_pos.data_ptr(), pages.data_ptr(),
                         T, ld, num_heads, num_kv_heads, head_dim, value_dim, half, pages.shape[-1],
                         1 if interleaved else 0, 1 if write_kv else 0, eps, q_scale, k_cache.shape[0],
                         q_temp[0] if q_temp is not None else 0.0, q_temp[1] if q_temp is not None else 0.0,
-                        1 if q_only else 0, 1 if head_unit else 0)
+                        1 if q_only else 0, 1 if head_unit else 0, _addr(talk), 1 if k_joined else 0)
     fn = _lib("qkv_cache.cu").gl_qkv_rownorm_cache
     _check(_launch(fn, byref(a), c_int(dtype_code(qkv.dtype)), c_int(dtype_code(k_cache.dtype)), _stream()),
            "qkv_rownorm_to_cache")
@@ -1304,7 +1313,7 @@ class _MixedAttnArgs(Structure):
                 ("T", c_int), ("B", c_int), ("nH", c_int), ("nKV", c_int), ("hd", c_int), ("vd", c_int),
                 ("max_pages", c_int), ("window", c_int), ("max_qlen", c_int), ("n_pages", c_int),
                 ("parts", c_void_p), ("ml", c_void_p), ("splits", c_int), ("pages_per_split", c_int),
-                ("score_scale", c_float), ("softcap", c_float), ("slopes", c_void_p), ("sinks", c_void_p)]
+                ("score_scale", c_float), ("softcap", c_float), ("slopes", c_void_p), ("sinks", c_void_p), ("nVH", c_int)]
 
 
 # A block of the one-token kernel walks its pages one after the other and waits for each: what hides the trips to
@@ -1327,7 +1336,7 @@ class _PairsArgs(Structure):
                 ("seq_qstart", c_void_p), ("seq_qlen", c_void_p), ("seq_ctx", c_void_p), ("pages", c_void_p),
                 ("B", c_int), ("nH", c_int), ("nKV", c_int), ("nVal", c_int), ("max_pages", c_int), ("window", c_int),
                 ("max_qlen", c_int), ("score_scale", c_float), ("softcap", c_float), ("slopes", c_void_p),
-                ("out", c_void_p), ("sinks", c_void_p)]
+                ("out", c_void_p), ("sinks", c_void_p), ("nVH", c_int)]
 
 
 USE_PAIRS_TC = True
@@ -1337,12 +1346,15 @@ def attention_mixed(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tenso
                     num_heads: int, num_kv_heads: int, head_dim: int, value_dim: int,
                     mix: Optional[torch.Tensor] = None, window: int = 0, score_scale: float = 1.0,
                     softcap: float = 0.0, slopes: Optional[torch.Tensor] = None,
-                    sinks: Optional[torch.Tensor] = None) -> torch.Tensor:
+                    sinks: Optional[torch.Tensor] = None, value_heads: int = 0) -> torch.Tensor:
     """Causal softmax attention of scaled queries [T, nH*hd] over the paged cache; with ``mix`` [nH, nH]
     head h applies sum_g mix[h, g] * (head g's softmax weights) to the values of its own key/value
     head.  A score is (q . k) * score_scale, then softcap * tanh(score / softcap) when softcap > 0, then
     minus slopes[h] * (query position - key position) when ``slopes`` [nH] float32 is given.  With ``sinks``
     [nH] float32 the denominator of head h's softmax also holds exp(sinks[h]), once, with no key and no value.
+    ``value_heads`` > 0: the value cache has that many heads (a multiple of the key heads), and without a table
+    query head h takes the values of head h / (nH / value_heads): many query heads on one wide key head, each
+    with one of several value heads.
     Returns [T, nH*vd] in q's type.  Prompts in bfloat16 with key and value sizes that are
     multiples of 16 compute the (query head, value head) pairs on the tensor cores (a library per pair
     of sizes); everything else runs the 32-bit kernels."""
@@ -1356,15 +1368,21 @@ def attention_mixed(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tenso
     if sinks is not None:
         _need(sinks, "sinks", torch.float32, (num_heads,))
     n_val = num_kv_heads if mix is not None else 1
+    nvh = int(value_heads)
+    if nvh and (nvh % num_kv_heads or num_heads % nvh or (mix is not None and nvh != num_kv_heads)):
+        raise KernelError(f"attention_mixed: {nvh} value heads do not fit {num_heads} query heads on {num_kv_heads} key heads")
+    if tuple(v_cache.shape[1:]) != (nvh or num_kv_heads, PAGE, value_dim) or tuple(k_cache.shape[1:]) != (num_kv_heads, PAGE, head_dim):
+        raise KernelError(f"attention_mixed: cache pages do not fit: keys {tuple(k_cache.shape)}, values {tuple(v_cache.shape)}")
     out = empty((T, num_heads * value_dim), q.dtype, q.device)
     pairs_tc = (USE_PAIRS_TC and ctx.max_qlen > 1 and q.dtype == torch.bfloat16 and k_cache.dtype == torch.bfloat16
-                and head_dim % 16 == 0 and value_dim % 16 == 0 and not DEBUG_BOUNDS)
+                and head_dim % 16 == 0 and value_dim % 16 == 0 and head_dim <= 256 and value_dim <= 256
+                and 3 * 64 * (2 * head_dim + 16) + 2 * 64 * (2 * value_dim + 16) <= 227 * 1024 and not DEBUG_BOUNDS)
     if pairs_tc and mix is None:
         # prompts without a mixing table: the tensor-core kernel rounds and writes the result itself
         p = _PairsArgs(q.data_ptr(), None, k_cache.data_ptr(), v_cache.data_ptr(),
                        ctx.seq_qstart.data_ptr(), ctx.seq_qlen.data_ptr(), ctx.seq_ctx.data_ptr(), pages.data_ptr(),
                        ctx.n_seqs, num_heads, num_kv_heads, 1, pages.shape[-1], window, ctx.max_qlen,
-                       score_scale, softcap, _addr(slopes), out.data_ptr(), _addr(sinks))
+                       score_scale, softcap, _addr(slopes), out.data_ptr(), _addr(sinks), nvh)
         fn = _lib("attention_mixed_tc.cu", catalog.pair_dim_defines(head_dim, value_dim)).gl_attention_pairs_tc
         _check(_launch(fn, byref(p), _stream()), "attention_pairs_tc")
         return out
@@ -1372,8 +1390,9 @@ def attention_mixed(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tenso
     a = _MixedAttnArgs(q.data_ptr(), pairs.data_ptr(), out.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), _addr(mix),
                        ctx.seq_qstart.data_ptr(), ctx.seq_qlen.data_ptr(), ctx.seq_ctx.data_ptr(), pages.data_ptr(),
                        T, ctx.n_seqs, num_heads, num_kv_heads, head_dim, value_dim, pages.shape[-1], window,
-                       ctx.max_qlen, k_cache.shape[0], None, None, 0, 0, score_scale, softcap, _addr(slopes), _addr(sinks))
-    if ctx.max_qlen == 1 and num_heads // num_kv_heads <= 8 and num_kv_heads <= 8 and value_dim <= 128:
+                       ctx.max_qlen, k_cache.shape[0], None, None, 0, 0, score_scale, softcap, _addr(slopes), _addr(sinks), nvh)
+    if (ctx.max_qlen == 1 and num_heads // num_kv_heads <= 8 and value_dim <= 128
+            and (num_kv_heads if mix is not None else (nvh or num_kv_heads) // num_kv_heads) <= 8):
         # one token a sequence: the context in ranges of pages, a block each (sized for the step's longest
         # sequence; a captured step is sized for its bucket's longest), put together by the mixing kernel
         splits = mixed_decode_splits(ctx.n_seqs, num_kv_heads, ctx.max_len, q.device)
@@ -1387,7 +1406,7 @@ def attention_mixed(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tenso
         p = _PairsArgs(q.data_ptr(), pairs.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(),
                        ctx.seq_qstart.data_ptr(), ctx.seq_qlen.data_ptr(), ctx.seq_ctx.data_ptr(), pages.data_ptr(),
                        ctx.n_seqs, num_heads, num_kv_heads, n_val, pages.shape[-1], window, ctx.max_qlen,
-                       score_scale, softcap, _addr(slopes), None, _addr(sinks))
+                       score_scale, softcap, _addr(slopes), None, _addr(sinks), nvh)
         fn = _lib("attention_mixed_tc.cu", catalog.pair_dim_defines(head_dim, value_dim)).gl_attention_pairs_tc
         _check(_launch(fn, byref(p), _stream()), "attention_pairs_tc")
         _check(_launch(lib.gl_head_mix, byref(a), c_int(dtype_code(q.dtype)), _stream()), "head_mix")
@@ -1397,16 +1416,110 @@ def attention_mixed(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tenso
     return out
 
 
-def gated_act(gu: torch.Tensor, act) -> torch.Tensor:
-    """act(gate) * up for rows that hold the gate's columns and then the up projection's."""
+def gated_act(gu: torch.Tensor, act, inner: Optional[int] = None, row_gate: Optional[int] = None) -> torch.Tensor:
+    """act(gate) * up for rows that hold the gate's columns and then the up projection's.  ``inner``: the rows
+    are longer than that, the gate's ``inner`` columns first, the up projection's behind them; ``row_gate``: the
+    column of such a row whose sigmoid multiplies the whole row's result."""
     _need(gu, "gu")
     T, F2 = gu.shape
+    if inner is not None:
+        if act not in ACTIVATIONS or 2 * inner > F2 or (row_gate is not None and not 0 <= row_gate < F2):
+            raise KernelError("gated_act: the rows do not hold the gate's and the up projection's columns")
+        out = empty((T, inner), gu.dtype, gu.device)
+        fn = _lib("rowwise.cu").gl_gated_act_rows
+        _check(_launch(fn, _ptr(gu), _ptr(out), c_int(T), c_int(inner), c_int(F2), c_int(-1 if row_gate is None else row_gate),
+                       c_int(ACTIVATIONS[act]), c_int(dtype_code(gu.dtype)), _stream()), "gated_act")
+        return out
     if F2 % 2 or act not in ACTIVATIONS:
         raise KernelError("gated_act: rows of gate and up columns and a known activation expected")
     out = empty((T, F2 // 2), gu.dtype, gu.device)
     fn = _lib("rowwise.cu").gl_gated_act
     _check(_launch(fn, _ptr(gu), _ptr(out), c_int(T), c_int(F2 // 2), c_int(ACTIVATIONS[act]),
                    c_int(dtype_code(gu.dtype)), _stream()), "gated_act")
+    return out
+
+
+def xielu(x: torch.Tensor, up: float, down: float) -> torch.Tensor:
+    """In place: up * z^2 + z / 2 above zero, down * (e^z - 1 - z) + z / 2 at and below it."""
+    _need(x, "x")
+    _check(_launch(_lib("rowwise.cu").gl_xielu, _ptr(x), ctypes.c_longlong(x.numel()), c_float(up), c_float(down),
+                   c_int(dtype_code(x.dtype)), _stream()), "xielu")
+    return x
+
+
+# ---------------------------------------------------------------------------
+# Attention through a latent (csrc/latent.cu)
+class _LatentPrepareArgs(Structure):
+    _fields_ = [("proj", c_void_p), ("cq_out", c_void_p), ("k_cache", c_void_p), ("v_cache", c_void_p),
+                ("cosv", c_void_p), ("sinv", c_void_p), ("q_gamma", c_void_p), ("kv_gamma", c_void_p),
+                ("tok_seq", c_void_p), ("tok_pos", c_void_p), ("pages", c_void_p),
+                ("T", c_int), ("ld", c_int), ("q_rank", c_int), ("kv_rank", c_int), ("rot", c_int), ("max_pages", c_int),
+                ("n_pages", c_int), ("interleaved", c_int), ("write_kv", c_int), ("eps", c_float)]
+
+
+def latent_prepare(proj: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, ctx, pages: torch.Tensor,
+                   q_rank: int, kv_rank: int, rot: int, q_gamma: torch.Tensor, kv_gamma: torch.Tensor, eps: float,
+                   cos: Optional[torch.Tensor], sin: Optional[torch.Tensor], interleaved: bool,
+                   write_kv: bool = True) -> torch.Tensor:
+    """A token's down projections proj [T, ld] = [query latent (q_rank) | c (kv_rank) | key part (rot) | ...]: both
+    latents RMS-normed with their weights (32-bit), the key part rotated by the token's angles; the row [c | key part]
+    goes to the token's place in k_cache [pages, 1, PAGE, kv_rank + rot], c to v_cache [pages, 1, PAGE, kv_rank].
+    Returns the normed query latent [T, q_rank]."""
+    _need(proj, "proj")
+    T, ld = proj.shape
+    if ld < q_rank + kv_rank + rot:
+        raise KernelError("latent_prepare: the projection's rows are too short")
+    if tuple(k_cache.shape[1:]) != (1, PAGE, kv_rank + rot) or tuple(v_cache.shape[1:]) != (1, PAGE, kv_rank):
+        raise KernelError(f"cache pages do not fit: keys {tuple(k_cache.shape)}, values {tuple(v_cache.shape)}")
+    _need(q_gamma, "q_gamma", torch.float32, (q_rank,))
+    _need(kv_gamma, "kv_gamma", torch.float32, (kv_rank,))
+    if cos is not None:
+        _need(cos, "cos", torch.float32, (T, rot // 2))
+        _need(sin, "sin", torch.float32, (T, rot // 2))
+    cq = empty((T, q_rank), proj.dtype, proj.device)
+    a = _LatentPrepareArgs(proj.data_ptr(), cq.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), _addr(cos), _addr(sin),
+                           q_gamma.data_ptr(), kv_gamma.data_ptr(), ctx.tok_seq.data_ptr(), ctx.tok_pos.data_ptr(),
+                           pages.data_ptr(), T, ld, q_rank, kv_rank, rot, pages.shape[-1], k_cache.shape[0],
+                           1 if interleaved else 0, 1 if write_kv else 0, eps)
+    _check(_launch(_lib("latent.cu").gl_latent_prepare, byref(a), c_int(dtype_code(proj.dtype)),
+                   c_int(dtype_code(k_cache.dtype)), _stream()), "latent_prepare")
+    return cq
+
+
+class _HeadLinearArgs(Structure):
+    _fields_ = [("x", c_void_p), ("w", c_void_p), ("out", c_void_p), ("gate", c_void_p), ("cosv", c_void_p), ("sinv", c_void_p),
+                ("T", c_int), ("H", c_int), ("N", c_int), ("K", c_int),
+                ("x_row", c_int), ("x_head", c_int), ("x_off", c_int), ("o_row", c_int), ("o_head", c_int), ("o_off", c_int),
+                ("g_row", c_int), ("g_off", c_int), ("tail", c_int), ("interleaved", c_int)]
+
+
+def head_linear(x: torch.Tensor, w: torch.Tensor, x_head: int, tail: int = 0, cos: Optional[torch.Tensor] = None,
+                sin: Optional[torch.Tensor] = None, interleaved: bool = False, gate: Optional[torch.Tensor] = None,
+                gate_off: int = 0) -> torch.Tensor:
+    """A product per head: out[t, h, :N] = w[h] x[t, h, :K] for x [T, H * x_head] (head h's K inputs start at column
+    h * x_head) and w [H, N, K].  ``tail`` > 0: the columns x[t, h, K:K + tail] are copied behind the result, turned by
+    the token's angles when cos/sin [T, tail / 2] are given; out is [T, H * (N + tail)].  ``gate`` [T, ld]: the result
+    of head h is multiplied by sigmoid(gate[t, gate_off + h])."""
+    _need(x, "x")
+    _need(w, "w")
+    T = x.shape[0]
+    H, N, K = w.shape
+    if x.shape[1] != H * x_head or K + tail > x_head:
+        raise KernelError(f"head_linear: x {tuple(x.shape)} does not hold {H} heads of {K} + {tail} columns")
+    if cos is not None:
+        _need(cos, "cos", torch.float32, (T, tail // 2))
+        _need(sin, "sin", torch.float32, (T, tail // 2))
+    g_row = 0
+    if gate is not None:
+        _need(gate, "gate", x.dtype)
+        g_row = gate.shape[1]
+        if gate.shape[0] != T or gate_off + H > g_row:
+            raise KernelError("head_linear: the gate's rows do not hold a column for every head")
+    out = empty((T, H * (N + tail)), x.dtype, x.device)
+    a = _HeadLinearArgs(x.data_ptr(), w.data_ptr(), out.data_ptr(), _addr(gate), _addr(cos), _addr(sin), T, H, N, K,
+                        x.shape[1], x_head, 0, H * (N + tail), N + tail, 0, g_row, gate_off, tail, 1 if interleaved else 0)
+    _check(_launch(_lib("latent.cu").gl_head_linear, byref(a), c_int(dtype_code(x.dtype)), c_int(dtype_code(w.dtype)),
+                   _stream()), "head_linear")
     return out
 
 
@@ -1417,21 +1530,34 @@ MOE_TILE_ROWS = 32
 
 class _RouteArgs(Structure):
     _fields_ = [("logits", c_void_p), ("ids", c_void_p), ("weights", c_void_p),
-                ("T", c_int), ("E", c_int), ("top", c_int), ("groups", c_int), ("keep", c_int), ("scale", c_float)]
+                ("T", c_int), ("E", c_int), ("top", c_int), ("groups", c_int), ("keep", c_int), ("scale", c_float),
+                ("bias", c_void_p), ("softmax_chosen", c_int)]
 
 
-def moe_route(logits: torch.Tensor, top: int, groups: int = 1, keep: int = 1, scale: float = 1.0):
+def _route_mode(E: int, groups: int, bias, softmax_chosen: bool) -> None:
+    if bias is not None:
+        _need(bias, "bias", torch.float32, (E,))
+    if softmax_chosen and groups != 1:
+        raise KernelError("moe_route: the softmax over the chosen logits takes one group of experts")
+
+
+def moe_route(logits: torch.Tensor, top: int, groups: int = 1, keep: int = 1, scale: float = 1.0,
+              bias: Optional[torch.Tensor] = None, softmax_chosen: bool = False):
     """Each token's ``top`` experts by sigmoid(logits) and their weights score / (sum of the chosen scores +
     1e-20) * scale: (ids int32 [T, top], weights float32 [T, top]).  With ``groups`` > 1 the experts form that
     many equal groups of neighbours; a group's score is the sum of its two largest scores and only experts of
-    the best ``keep`` groups are chosen from."""
+    the best ``keep`` groups are chosen from.  ``bias`` [E] float32 is added to the logits first.  With
+    ``softmax_chosen`` the ``top`` largest logits are chosen instead and weighted by the softmax over those
+    alone (times scale)."""
     _need(logits, "logits", torch.float32)
     T, E = logits.shape
+    _route_mode(E, groups, bias, softmax_chosen)
     if not (0 < top <= E and groups >= 1 and E % groups == 0 and 1 <= keep <= groups and keep * (E // groups) >= top):
         raise KernelError(f"moe_route: top {top} of {E} experts in {groups} groups of which {keep} stay is not possible")
     ids = empty((T, top), torch.int32, logits.device)
     weights = empty((T, top), torch.float32, logits.device)
-    a = _RouteArgs(logits.data_ptr(), ids.data_ptr(), weights.data_ptr(), T, E, top, groups, keep, scale)
+    a = _RouteArgs(logits.data_ptr(), ids.data_ptr(), weights.data_ptr(), T, E, top, groups, keep, scale, _addr(bias),
+                   1 if softmax_chosen else 0)
     _check(_launch(_lib("moe.cu").gl_moe_route, byref(a), _stream()), "moe_route")
     return ids, weights
 
@@ -1441,10 +1567,12 @@ class _RouteFromArgs(Structure):
     # that a tape of launches finds every pointer)
     _fields_ = [("x", c_void_p), ("w", c_void_p), ("K", c_int),
                 ("logits", c_void_p), ("ids", c_void_p), ("weights", c_void_p),
-                ("T", c_int), ("E", c_int), ("top", c_int), ("groups", c_int), ("keep", c_int), ("scale", c_float)]
+                ("T", c_int), ("E", c_int), ("top", c_int), ("groups", c_int), ("keep", c_int), ("scale", c_float),
+                ("bias", c_void_p), ("softmax_chosen", c_int)]
 
 
-def moe_route_from(x: torch.Tensor, w_router: torch.Tensor, top: int, groups: int = 1, keep: int = 1, scale: float = 1.0):
+def moe_route_from(x: torch.Tensor, w_router: torch.Tensor, top: int, groups: int = 1, keep: int = 1, scale: float = 1.0,
+                   bias: Optional[torch.Tensor] = None, softmax_chosen: bool = False):
     """``moe_route`` of the logits x . w_router^T ([T, K] in the activation type, [E, K] float32) in one kernel:
     a token's logits are sums over k in an order of their own, whatever else is in the step.  Inputs too wide
     for a block's shared memory take the plain product and ``moe_route``."""
@@ -1454,14 +1582,15 @@ def moe_route_from(x: torch.Tensor, w_router: torch.Tensor, top: int, groups: in
     E = w_router.shape[0]
     if w_router.shape[1] != K:
         raise KernelError(f"moe_route_from: router {tuple(w_router.shape)} does not fit x {tuple(x.shape)}")
+    _route_mode(E, groups, bias, softmax_chosen)
     if (E + groups + K) * 4 > 48 * 1024:
-        return moe_route(gemm_simt(x, w_router, out_dtype=torch.float32), top, groups, keep, scale)
+        return moe_route(gemm_simt(x, w_router, out_dtype=torch.float32), top, groups, keep, scale, bias, softmax_chosen)
     if not (0 < top <= E and groups >= 1 and E % groups == 0 and 1 <= keep <= groups and keep * (E // groups) >= top):
         raise KernelError(f"moe_route: top {top} of {E} experts in {groups} groups of which {keep} stay is not possible")
     ids = empty((T, top), torch.int32, x.device)
     weights = empty((T, top), torch.float32, x.device)
     a = _RouteFromArgs(x.data_ptr(), w_router.data_ptr(), K, None, ids.data_ptr(), weights.data_ptr(), T, E, top, groups,
-                       keep, scale)
+                       keep, scale, _addr(bias), 1 if softmax_chosen else 0)
     _check(_launch(_lib("moe.cu").gl_moe_route_from, byref(a), c_int(dtype_code(x.dtype)), _stream()), "moe_route")
     return ids, weights
 

@@ -42,6 +42,7 @@ class KVRequest:
     head_dim: int
     window: int = 0
     value_dim: int = 0        # size of a head's values where it differs from head_dim (0: the same)
+    value_heads: int = 0      # rows of values per position where they differ from the rows of keys (0: the same)
 
 
 @dataclass(frozen=True)

@@ -201,7 +201,8 @@ class PostNormBlock(AssembledBlock):
     the activation type where that is not 32-bit) and what they return is RMS-normed before it is added.  A layer
     without a feed-forward (``spec.ffn`` None, no norm2) is the first half alone.  A mixer that offers
     ``branches`` (two outputs with a factor each) is summed in the pass that norms and adds; that pass also
-    leaves the stream's rounded copy for the feed-forward."""
+    leaves the stream's rounded copy for the feed-forward.  Option ``branch_scale`` m: x <- x + m * norm(...) for
+    both sublayers (the factor is taken into the norms' weights once, when they are loaded)."""
 
     def __init__(self, spec: BlockSpec):
         if (spec.ffn is None) != (spec.norm2 is None):
@@ -210,10 +211,21 @@ class PostNormBlock(AssembledBlock):
         for n in (self.norm, self.norm2):
             if n is not None and not (getattr(n, "rms", False) and n.fusable is not None and not n.spec.bias):
                 raise ValueError("a block that norms its sublayers' outputs takes RMS norms without bias")
+        self.branch_scale = float(spec.option("branch_scale", 1.0))
+        self.w1 = self.w2 = None                 # the norms' weights times the factor
+
+    def load(self, tensors: Dict[str, torch.Tensor]) -> None:
+        super().load(tensors)
+        if self.branch_scale != 1.0:
+            self.w1 = (self.norm.fusable()[0] * self.branch_scale).contiguous()
+            if self.norm2 is not None:
+                self.w2 = (self.norm2.fusable()[0] * self.branch_scale).contiguous()
 
     def forward(self, x, ctx, cache):
         h = ops.round_rows(x, ctx.act_dtype)
         w, _, eps, _ = self.norm.fusable()
+        if self.w1 is not None:
+            w = self.w1
         copy = ctx.act_dtype if self.ffn is not None and ctx.act_dtype != torch.float32 else None
         branches = getattr(self.mixer, "branches", None)
         if branches is not None:
@@ -225,6 +237,8 @@ class PostNormBlock(AssembledBlock):
         if self.ffn is None:
             return x
         w2, _, eps2, _ = self.norm2.fusable()
+        if self.w2 is not None:
+            w2 = self.w2
         y = self.ffn.forward(h if h is not None else x, ctx, (), None)
         ops.post_norm_add(y, w2, eps2, add=x, out=x)
         return x

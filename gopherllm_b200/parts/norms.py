@@ -24,13 +24,16 @@ class LayerNorm(Norm):
 
     def parameters(self) -> Dict[str, ParamSpec]:
         # (a weight stored as its distance from weight_offset is drawn around zero in the random-weights mode)
-        p = {"weight": ParamSpec((self.spec.dim,), "vector", "bias" if self.spec.weight_offset else "gamma")}
+        shape = () if self.spec.single_weight else (self.spec.dim,)
+        p = {"weight": ParamSpec(shape, "vector", "bias" if self.spec.weight_offset else "gamma")}
         if self.spec.bias:
             p["bias"] = ParamSpec((self.spec.dim,), "vector", "beta")
         return p
 
     def load(self, tensors: Dict[str, torch.Tensor]) -> None:
         self.weight = tensors["weight"]
+        if self.spec.single_weight:                  # one number for all coordinates: the kernels take a vector
+            self.weight = self.weight.reshape(1).expand(self.spec.dim).contiguous()
         if self.spec.weight_offset:
             self.weight = (self.weight + float(self.spec.weight_offset)).contiguous()
         self.bias = tensors.get("bias")
