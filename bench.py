@@ -6,6 +6,7 @@
     python bench.py --ragged                 64 unequal prompts as one batch through Model.generate
     python bench.py --design gozolix         the same for a Gozolix model, beside a Vopedra model of equal width and depth
     python bench.py --design lilupel         the same for a Lilupel model, beside a Vopedra model of equal width and depth
+    python bench.py --design darusun         the same for a Darusun model, beside a Gozolix model of equal width and depth
     python bench.py --design vopedra         prefill and decode of a Vopedra model at a few layer sizes beside a
                                              Phi model of equal width, depth and feed-forward weights
 
@@ -119,7 +120,7 @@ def main():
     ap.add_argument("--sections", default="decode,e2e,prefill,points",
                     help="which measurements to run (for profiling a part): decode,e2e,prefill,points")
     ap.add_argument("--model", default="phi-2", choices=sorted(MODELS), help="whose layer sizes to run")
-    ap.add_argument("--design", default=None, choices=["vopedra", "gozolix", "lilupel"],
+    ap.add_argument("--design", default=None, choices=["vopedra", "gozolix", "lilupel", "darusun"],
                     help="instead: prefill and decode rates of another design at a few layer sizes, beside the Phi "
                          "model of equal width and depth")
     ap.add_argument("--ragged", action="store_true",
@@ -149,7 +150,7 @@ def main():
 
     if args.design == "vopedra":
         return design_vopedra(args)
-    if args.design in ("gozolix", "lilupel"):
+    if args.design in ("gozolix", "lilupel", "darusun"):
         return design_vopedra(args, design=args.design)
     pk, pk_src = peaks()
     label, sizes, weight_seed = MODELS[args.model]
@@ -382,11 +383,35 @@ def lilupel_sizes(width, heads, ff):
             "layers": five + second}
 
 
+def darusun_sizes(width, heads, ff):
+    """A Darusun model whose layers resemble a real model's at this width, ten layers: attention through a latent
+    (192 + 64 numbers a position, a window of 512) with a dense feed-forward, attention with mixed scores on four
+    key/value heads with a mixture of 32 experts (4 a token, and a gated shared one), attention on that layer's keys
+    with a mixture, latent attention with a mixture, mixed-score attention with a dense feed-forward; twice.  A token
+    meets about as many feed-forward weights in every layer as in the other designs."""
+    hd = width // heads
+    latent = {"heads": heads, "dim": hd, "rot_dim": 64, "vdim": hd, "q_rank": 3 * width // 4, "kv_rank": 192,
+              "scale": (hd + 64) ** -0.5, "mask": {"size": 512}, "rot": {"dims": 64, "base": 10000.0}}
+    attn = {"heads": heads, "kv_heads": min(4, heads), "dim": hd, "vdim": hd, "scale": 0.12,
+            "rot": {"dims": hd // 2, "base": 1000000.0}}
+    dense = {"kind": "dense", "ff": (3 * ff // 2) // 64 * 64}
+    moe = {"kind": "moe", "expert": {"ff": max(64, ff // 8 // 64 * 64)}, "shared": {"ff": ff // 2 // 64 * 64},
+           "router": {"experts": 32, "top": 4}}
+    five = [{"type": "latent_attention", "mixer": latent, "mlp": dense}, {"type": "attention", "mixer": attn, "mlp": moe},
+            {"type": "attention", "mixer": dict(attn, kv_from=1), "mlp": moe},
+            {"type": "latent_attention", "mixer": latent, "mlp": moe}, {"type": "attention", "mixer": attn, "mlp": dense}]
+    second = json.loads(json.dumps(five))
+    second[2]["mixer"]["kv_from"] = 6
+    return {"architecture": "Darusun", "vocab": 32000, "width": width, "norm": {"eps": 1e-6}, "residual_mult": 0.7,
+            "initializer_range": 0.02, "layers": five + second}
+
+
 def design_vopedra(args, design="vopedra"):
     """Prefill and decode rates of Vopedra models (random weights) beside Phi models of the same width, the
     same number of layer runs and feed-forwards of the same number of weights; with ``design`` "gozolix" or
-    "lilupel", of models of that design beside Vopedra models of the same width and number of layer runs.  One
-    JSON line."""
+    "lilupel", of models of that design beside Vopedra models of the same width and number of layer runs; with
+    "darusun", beside Gozolix models (the nearest relative: softmax attention, layers on another layer's keys, dense
+    feed-forwards and routed mixtures with a shared expert).  One JSON line."""
     import numpy as np
     import torch
     import gopherllm_b200 as gl
@@ -447,6 +472,10 @@ def design_vopedra(args, design="vopedra"):
     clocks.start()
     rows = []
     for width, heads, ff_gated, ff_plain in ((1024, 16, 2752, 4096), (2048, 32, 5504, 8192)):
+        if design == "darusun":
+            rows.append({"width": width, "heads": heads, design: measure(darusun_sizes(width, heads, ff_gated)),
+                         "gozolix": measure(gozolix_sizes(width, heads, ff_gated))})
+            continue
         if design in ("gozolix", "lilupel"):
             sizes = gozolix_sizes if design == "gozolix" else lilupel_sizes
             rows.append({"width": width, "heads": heads, design: measure(sizes(width, heads, ff_gated)),
@@ -456,8 +485,9 @@ def design_vopedra(args, design="vopedra"):
         phi = dict(PHI15, hidden_size=width, num_attention_heads=heads, num_key_value_heads=heads,
                    intermediate_size=ff_plain, vocab_size=32000, num_hidden_layers=v["layer_runs"])
         rows.append({"width": width, "heads": heads, "vopedra": v, "phi": measure(phi)})
-    if design in ("gozolix", "lilupel"):
-        print(json.dumps({"metric": f"prefill and decode rates of {design.capitalize()} layer sizes beside Vopedra of equal width and depth (bf16)",
+    if design in ("gozolix", "lilupel", "darusun"):
+        beside = "Gozolix" if design == "darusun" else "Vopedra"
+        print(json.dumps({"metric": f"prefill and decode rates of {design.capitalize()} layer sizes beside {beside} of equal width and depth (bf16)",
                           "unit": "tokens/s", "n_gpus": 1, "dtype": "bf16", "data": "synthetic: random weights seed 7, uniform token ids",
                           "decode_steps_timed": K, "decode_context": 1024, "peaks": pk_src, "clocks": clocks.stop(), "sizes": rows}))
         return 0

@@ -257,7 +257,8 @@ attn_pairs_decode_kernel(MixedAttnArgs a) {
 }
 
 // One token a sequence, few heads a group: a block owns one key head of one sequence, that is the query
-// heads that share it, and every value head their weights are applied to.  A page of keys is read once
+// heads that share it (up to eight; where more share a key head, as when every head reads one wide key row, a
+// block owns a run of eight of them), and every value head their weights are applied to.  A page of keys is read once
 // for all of the group's query heads (a thread a (head, key) score), the softmax of a head is kept by one
 // warp, and each warp accumulates one value head for all of the group's query heads, so a page of values
 // is read once per key head and not once per pair.
@@ -294,26 +295,30 @@ attn_group_decode_kernel(MixedAttnArgs a) {
     gl_grid_launch_dependents();
     gl_grid_wait();
     const int hd = a.hd, vd = a.vd;
-    const int gq = a.nH / a.nKV;                        // query heads of the group (<= GQ)
+    const int group = a.nH / a.nKV;                     // query heads of a key head
+    const int gq = group < GQ ? group : GQ;             // of this block (<= GQ); group is a multiple of it
+    const int chunks = group / gq;
     float* qv = smem;                                   // [gq][hd]
     float* sc = qv + gq * hd;                           // [gq][GL_PAGE] scores, then weights
     float* corr = sc + gq * GL_PAGE;                    // [gq] rescaling of this page, then 1 / sum
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int b = blockIdx.y, kh = blockIdx.x, split = blockIdx.z;
+    const int b = blockIdx.y, kh = blockIdx.x / chunks, split = blockIdx.z;
+    const int head0 = kh * group + (blockIdx.x - kh * chunks) * gq;      // this block's first query head
     const int nVal = a.mix ? a.nKV : 1;
     const int p = a.seq_ctx[b];
     const int lo = (a.window > 0 && p - a.window + 1 > 0) ? p - a.window + 1 : 0;
     const int row = a.seq_qstart[b];
     const int page_first = lo / GL_PAGE + split * a.pages_per_split;
     const int page_last = min(p / GL_PAGE, page_first + a.pages_per_split - 1);      // may lie before page_first: nothing to do
-    const TA* qsrc = (const TA*)a.q + ((size_t)row * a.nH + (size_t)kh * gq) * hd;
+    const TA* qsrc = (const TA*)a.q + ((size_t)row * a.nH + (size_t)head0) * hd;
     for (int i = threadIdx.x; i < gq * hd; i += AM_GTHREADS) qv[i] = gl_load(qsrc + i);
     // this warp's value head: with a table every value head meets every query head; without one the key head's
     // query heads fall into as many equal runs as it has value heads, a warp a run
     const int nvh = am_value_heads(a);
-    const int runs = a.mix ? 1 : nvh / a.nKV;           // value heads of this key head
-    const int per = gq / runs;                          // query heads that share one of them
-    const int vh = a.mix ? warp : kh * runs + warp;
+    const int share = a.nH / nvh;                       // query heads that share a value head
+    const int per = share < gq ? share : gq;            // ... among this block's
+    const int runs = a.mix ? 1 : gq / per;              // value heads of this block
+    const int vh = a.mix ? warp : head0 / share + warp;
     const bool has_values = a.mix ? warp < a.nKV : warp < runs;
     float acc[GQ][NACC];
 #pragma unroll
@@ -331,7 +336,7 @@ attn_group_decode_kernel(MixedAttnArgs a) {
             const int g = item / GL_PAGE, key = item - g * GL_PAGE;
             const int j = j0 + key;
             sc[item] = (j >= lo && j <= p)
-                ? am_shape(am_dot(qv + g * hd, kp + (size_t)key * hd, hd), a, a.slopes ? a.slopes[kh * gq + g] : 0.f, p, j)
+                ? am_shape(am_dot(qv + g * hd, kp + (size_t)key * hd, hd), a, a.slopes ? a.slopes[head0 + g] : 0.f, p, j)
                 : -INFINITY;
         }
         __syncthreads();
@@ -389,7 +394,7 @@ attn_group_decode_kernel(MixedAttnArgs a) {
     }
     // the range's sums as they are, with its maximum and sum: the mixing kernel puts the ranges together
     if (warp < gq && lane == 0) {
-        float* dst = a.ml + (((size_t)b * a.nH + (size_t)kh * gq + warp) * a.splits + split) * 2;
+        float* dst = a.ml + (((size_t)b * a.nH + (size_t)head0 + warp) * a.splits + split) * 2;
         dst[0] = m;
         dst[1] = l;
     }
@@ -397,7 +402,7 @@ attn_group_decode_kernel(MixedAttnArgs a) {
 #pragma unroll
         for (int g = 0; g < GQ; ++g) {
             if (g < gq && (a.mix || g / per == warp)) {
-                float* o = a.parts + ((((size_t)b * a.nH + (size_t)kh * gq + g) * nVal + (a.mix ? vh : 0)) * a.splits + split) * vd;
+                float* o = a.parts + ((((size_t)b * a.nH + (size_t)head0 + g) * nVal + (a.mix ? vh : 0)) * a.splits + split) * vd;
 #pragma unroll
                 for (int i = 0; i < NACC; ++i) {
                     const int d = lane + 32 * i;
@@ -449,9 +454,9 @@ head_mix_split_kernel(MixedAttnArgs a) {
 
 template <typename TA, typename TC, int NACC>
 static int launch_group_decode(const MixedAttnArgs& a, cudaStream_t stream) {
-    const int gq = a.nH / a.nKV;
+    const int group = a.nH / a.nKV, gq = group < 8 ? group : 8;
     const size_t smem = ((size_t)gq * a.hd + (size_t)gq * GL_PAGE + gq) * sizeof(float);
-    const dim3 grid(a.nKV, a.B, a.splits);
+    const dim3 grid(a.nKV * (group / gq), a.B, a.splits);
     if (gq <= 1) return gl_launch(attn_group_decode_kernel<TA, TC, NACC, 1>, grid, dim3(AM_GTHREADS), smem, stream, 1, a);
     if (gq <= 2) return gl_launch(attn_group_decode_kernel<TA, TC, NACC, 2>, grid, dim3(AM_GTHREADS), smem, stream, 1, a);
     if (gq <= 4) return gl_launch(attn_group_decode_kernel<TA, TC, NACC, 4>, grid, dim3(AM_GTHREADS), smem, stream, 1, a);
@@ -486,8 +491,13 @@ template <typename TA, typename TC, int NACC>
 static int launch_mixed(const MixedAttnArgs& a, cudaStream_t stream) {
     const int pairs = a.nH * (a.mix ? a.nKV : 1);
     int rc;
-    if (a.max_qlen == 1 && a.nH / a.nKV <= 8 && (a.mix ? a.nKV : am_value_heads(a) / a.nKV) <= AM_GTHREADS / 32 && NACC <= 4 &&
-        a.parts && a.ml && a.splits > 0) {
+    // the kernel by key head: with a table every query head of the key head in one block (up to eight, and a warp a
+    // value head); without one, runs of eight query heads whose value heads are whole within a run or span whole runs
+    const int group = a.nH / a.nKV, share = a.nH / am_value_heads(a);
+    const bool by_key_head = a.mix ? (group <= 8 && a.nKV <= AM_GTHREADS / 32)
+                                   : (group <= 8 ? group % (share < group ? share : group) == 0
+                                                 : (group % 8 == 0 && (share >= 8 ? share % 8 == 0 : 8 % share == 0)));
+    if (a.max_qlen == 1 && by_key_head && NACC <= 4 && a.parts && a.ml && a.splits > 0) {
         rc = launch_group_decode<TA, TC, NACC>(a, stream);
         if (rc != 0) return rc;
         return gl_launch(head_mix_split_kernel<TA>, dim3(a.nH, a.B), dim3(a.vd <= 64 ? 64 : 128), (size_t)(a.mix ? a.nH : 1) * a.splits * sizeof(float), stream, 1, a);
@@ -508,6 +518,20 @@ static int launch_mixed(const MixedAttnArgs& a, cudaStream_t stream) {
     if (rc != 0) return rc;
     const long long n = (long long)a.T * a.nH * a.vd;
     return gl_launch(head_mix_kernel<TA>, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, stream, 1, a);
+}
+
+// the kernel that puts a one-token step's ranges together, behind a kernel of another library that left them
+GL_API int gl_head_mix_split(const MixedAttnArgs* args, int act_dtype, cudaStream_t stream) {
+    const MixedAttnArgs& a = *args;
+    if (a.B <= 0) return GL_OK;
+    if (!a.parts || !a.ml || a.splits <= 0 || a.vd <= 0) return GL_ERR_SHAPE;
+    const dim3 grid(a.nH, a.B), block(a.vd <= 64 ? 64 : 128);
+    const size_t smem = (size_t)(a.mix ? a.nH : 1) * a.splits * sizeof(float);
+    int rc;
+    if (act_dtype == GL_F32) rc = gl_launch(head_mix_split_kernel<float>, grid, block, smem, stream, 1, a);
+    else if (act_dtype == GL_BF16) rc = gl_launch(head_mix_split_kernel<__nv_bfloat16>, grid, block, smem, stream, 1, a);
+    else return GL_ERR_DTYPE;
+    return rc == 0 ? GL_OK : GL_ERR_LAUNCH;
 }
 
 // the mixing kernel alone, behind a pairs kernel of another library

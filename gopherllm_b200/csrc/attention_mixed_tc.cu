@@ -314,6 +314,233 @@ attn_pairs_tc_kernel(PairsArgs a) {
     }
 }
 
+// ---------------------------------------------------------------------------
+// One token a sequence, many query heads on one key head (every head of a mixer that reads one wide key row per
+// position): the heads are the rows of the score product.  A block takes a run of up to 16 query heads that share a
+// value head, one sequence and a range of its pages; K and V pages stream through shared memory with cp.async, two
+// in flight; warp w owns keys 16w..16w+15 of every page with a running softmax of its own, S = Q K^T and O += P V on
+// mma.sync.m16n8k16, 32-bit softmax; the four warps' results are put together in shared memory and leave as the
+// range's sums not yet divided, with its maximum and sum, for the kernel that merges the ranges
+// (head_mix_split_kernel in attention_mixed.cu, which also knows the sinks).  With v_in_k the values are the first
+// AP_VD columns of the key rows and no value page is fetched at all.
+// ---------------------------------------------------------------------------
+struct RowsDecodeArgs {
+    const void* q;            // [B rows, nH*hd] bf16
+    const void* k_cache;      // [pages, nKV, GL_PAGE, hd] bf16
+    const void* v_cache;      // [pages, nVH, GL_PAGE, vd] bf16 (unused with v_in_k)
+    const int* seq_qstart;
+    const int* seq_ctx;
+    const int* pages;         // [B, max_pages]
+    float* parts;             // [B, nH, 1, splits, vd] sums not yet divided
+    float* ml;                // [B, nH, splits, 2] each range's maximum and sum
+    int B, nH, nKV, nVH, max_pages, window, splits, pages_per_split, rows, v_in_k;
+    float score_scale;
+};
+
+__global__ void __launch_bounds__(AP_THREADS)
+attn_rows_decode_tc_kernel(RowsDecodeArgs a) {
+    extern __shared__ __align__(16) unsigned char smem[];
+    constexpr int QT = 16 * AP_ROW;
+    const unsigned sQ = ap_smem(smem);
+    const unsigned sK[2] = {sQ + QT, sQ + QT + AP_TILE};
+    const unsigned sV[2] = {sQ + QT + 2 * AP_TILE, sQ + QT + 2 * AP_TILE + AP_VTILE};
+    gl_grid_launch_dependents();
+    gl_grid_wait();
+    const int b = blockIdx.y, split = blockIdx.z;
+    const int head0 = blockIdx.x * a.rows;
+    const int kh = head0 / (a.nH / a.nKV), vh = head0 / (a.nH / a.nVH);
+    const int p = a.seq_ctx[b];                                   // the token's position; keys lo..p
+    const int lo = (a.window > 0 && p - a.window + 1 > 0) ? p - a.window + 1 : 0;
+    const int page_first = lo / GL_PAGE + split * a.pages_per_split;
+    const int page_last = min(p / GL_PAGE, page_first + a.pages_per_split - 1);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int grp = lane >> 2, t = lane & 3;
+    const int* pg = a.pages + (size_t)b * a.max_pages;
+    const __nv_bfloat16* K = (const __nv_bfloat16*)a.k_cache;
+    const __nv_bfloat16* V = (const __nv_bfloat16*)a.v_cache;
+    const size_t head_off = (size_t)kh * GL_PAGE * AP_HD, page_stride = (size_t)a.nKV * GL_PAGE * AP_HD;
+    const size_t vhead_off = (size_t)vh * GL_PAGE * AP_VD, vpage_stride = (size_t)a.nVH * GL_PAGE * AP_VD;
+
+    // the run's queries: rows of heads; rows past the run are zero
+    {
+        const __nv_bfloat16* src = (const __nv_bfloat16*)a.q + ((size_t)a.seq_qstart[b] * a.nH + head0) * AP_HD;
+        constexpr int CHUNKS = AP_HD / 8;
+        for (int i = threadIdx.x; i < 16 * CHUNKS; i += AP_THREADS) {
+            const int r = i / CHUNKS, c = i - r * CHUNKS;
+            const bool ok = r < a.rows;
+            ap_cp16(sQ + r * AP_ROW + c * 16, ok ? (const void*)(src + (size_t)r * AP_HD + c * 8) : (const void*)src, ok ? 16 : 0);
+        }
+    }
+    auto fetch = [&](int page_i, int st) {
+        const int nv = min(GL_PAGE, p + 1 - page_i * GL_PAGE);    // keys past p were never written
+        ap_load_rows<AP_HD>(sK[st], K + (size_t)pg[page_i] * page_stride + head_off, AP_HD, nv);
+        if (!a.v_in_k) ap_load_rows<AP_VD>(sV[st], V + (size_t)pg[page_i] * vpage_stride + vhead_off, AP_VD, nv);
+    };
+    if (page_first <= page_last) fetch(page_first, 0);
+    ap_commit();
+
+    float o[AP_NT][4];
+#pragma unroll
+    for (int i = 0; i < AP_NT; ++i)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) o[i][e] = 0.f;
+    float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+    const float LOG2E = 1.4426950408889634f;
+
+    for (int pi = page_first; pi <= page_last; ++pi) {
+        const int st = (pi - page_first) & 1;
+        if (pi + 1 <= page_last) fetch(pi + 1, st ^ 1);
+        ap_commit();
+        ap_wait<1>();
+        __syncthreads();
+        const int j0 = pi * GL_PAGE + warp * 16;                   // this warp's first key of the page
+        if (j0 <= p && j0 + 15 >= lo) {
+            float s[2][4];
+#pragma unroll
+            for (int j = 0; j < 2; ++j)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) s[j][e] = 0.f;
+#pragma unroll
+            for (int kk = 0; kk < AP_KS; ++kk) {
+                unsigned qf[4], b0, b1, b2, b3;
+                {
+                    const int r = (lane & 7) + ((lane >> 3) & 1) * 8;
+                    const int c = kk * 2 + (lane >> 4);
+                    ap_ldm4(sQ + r * AP_ROW + c * 16, qf[0], qf[1], qf[2], qf[3]);
+                }
+                const int r = warp * 16 + ((lane >> 4) & 1) * 8 + (lane & 7);
+                const int c = kk * 2 + ((lane >> 3) & 1);
+                ap_ldm4(sK[st] + r * AP_ROW + c * 16, b0, b1, b2, b3);
+                ap_mma(s[0], qf, b0, b1);
+                ap_mma(s[1], qf, b2, b3);
+            }
+            float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+            for (int j = 0; j < 2; ++j)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const int key = j0 + j * 8 + 2 * t + (e & 1);
+                    const float x = (key >= lo && key <= p) ? s[j][e] * a.score_scale : -INFINITY;
+                    s[j][e] = x;
+                    mx[e >> 1] = fmaxf(mx[e >> 1], x);
+                }
+#pragma unroll
+            for (int i = 0; i < 2; ++i) {
+                mx[i] = fmaxf(mx[i], __shfl_xor_sync(0xffffffffu, mx[i], 1));
+                mx[i] = fmaxf(mx[i], __shfl_xor_sync(0xffffffffu, mx[i], 2));
+            }
+            float corr[2], mu[2];
+#pragma unroll
+            for (int i = 0; i < 2; ++i) {
+                const float m_new = fmaxf(m_run[i], mx[i]);
+                mu[i] = (m_new == -INFINITY) ? 0.f : m_new * LOG2E;
+                corr[i] = exp2f(m_run[i] * LOG2E - mu[i]);          // m_run = -inf gives 0
+                m_run[i] = m_new;
+                l_run[i] *= corr[i];
+            }
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+                s[j][0] = exp2f(s[j][0] * LOG2E - mu[0]);
+                s[j][1] = exp2f(s[j][1] * LOG2E - mu[0]);
+                s[j][2] = exp2f(s[j][2] * LOG2E - mu[1]);
+                s[j][3] = exp2f(s[j][3] * LOG2E - mu[1]);
+                l_run[0] += s[j][0] + s[j][1];
+                l_run[1] += s[j][2] + s[j][3];
+            }
+#pragma unroll
+            for (int i = 0; i < AP_NT; ++i) {
+                o[i][0] *= corr[0]; o[i][1] *= corr[0];
+                o[i][2] *= corr[1]; o[i][3] *= corr[1];
+            }
+            unsigned pa[4];
+            pa[0] = ap_pack(s[0][0], s[0][1]);
+            pa[1] = ap_pack(s[0][2], s[0][3]);
+            pa[2] = ap_pack(s[1][0], s[1][1]);
+            pa[3] = ap_pack(s[1][2], s[1][3]);
+            const unsigned vbase = a.v_in_k ? sK[st] : sV[st];
+            const int vrow = a.v_in_k ? AP_ROW : AP_VROW;
+#pragma unroll
+            for (int dn = 0; dn < AP_NT; dn += 2) {
+                unsigned b0, b1, b2, b3;
+                const int r = warp * 16 + ((lane >> 3) & 1) * 8 + (lane & 7);
+                const int c = dn + (lane >> 4);
+                ap_ldm4t(vbase + r * vrow + c * 16, b0, b1, b2, b3);
+                ap_mma(o[dn], pa, b0, b1);
+                ap_mma(o[dn + 1], pa, b2, b3);
+            }
+        }
+        __syncthreads();
+    }
+    ap_wait<0>();
+    __syncthreads();
+    // the four warps' sums, maxima and sums of weights side by side in shared memory (over the page stages)
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        l_run[i] += __shfl_xor_sync(0xffffffffu, l_run[i], 1);
+        l_run[i] += __shfl_xor_sync(0xffffffffu, l_run[i], 2);
+    }
+    float* po = (float*)(smem + QT);                              // [4][16][AP_VD]
+    float* pm = po + 4 * 16 * AP_VD;                              // [4][16][2]
+#pragma unroll
+    for (int i = 0; i < AP_NT; ++i) {
+        const int d = i * 8 + 2 * t;
+        *(float2*)(po + ((size_t)warp * 16 + grp) * AP_VD + d) = make_float2(o[i][0], o[i][1]);
+        *(float2*)(po + ((size_t)warp * 16 + grp + 8) * AP_VD + d) = make_float2(o[i][2], o[i][3]);
+    }
+    if (t == 0) {
+        pm[(warp * 16 + grp) * 2] = m_run[0];
+        pm[(warp * 16 + grp) * 2 + 1] = l_run[0];
+        pm[(warp * 16 + grp + 8) * 2] = m_run[1];
+        pm[(warp * 16 + grp + 8) * 2 + 1] = l_run[1];
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < a.rows * AP_VD; i += AP_THREADS) {
+        const int r = i / AP_VD, d = i - r * AP_VD;
+        float mm = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) mm = fmaxf(mm, pm[(w * 16 + r) * 2]);
+        float y = 0.f, l = 0.f;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) {
+            const float mw = pm[(w * 16 + r) * 2];
+            if (mw > -INFINITY) {
+                const float f = expf(mw - mm);
+                y = fmaf(po[((size_t)w * 16 + r) * AP_VD + d], f, y);
+                l = fmaf(pm[(w * 16 + r) * 2 + 1], f, l);
+            }
+        }
+        a.parts[(((size_t)b * a.nH + head0 + r) * a.splits + split) * AP_VD + d] = y;
+        if (d == 0) {
+            float* dst = a.ml + (((size_t)b * a.nH + head0 + r) * a.splits + split) * 2;
+            dst[0] = mm;
+            dst[1] = l;
+        }
+    }
+}
+
+GL_API int gl_attention_rows_decode_tc(const RowsDecodeArgs* args, cudaStream_t stream) {
+    const RowsDecodeArgs& a = *args;
+    if (a.B <= 0) return GL_OK;
+    if (a.nH <= 0 || a.nKV <= 0 || a.nVH <= 0 || a.nH % a.nKV || a.nH % a.nVH || a.rows <= 0 || a.rows > 16 || a.nH % a.rows ||
+        (a.nH / a.nVH) % a.rows || (a.nH / a.nKV) % a.rows || a.splits <= 0 || a.pages_per_split <= 0) return GL_ERR_SHAPE;
+    if (a.v_in_k && (AP_VD > AP_HD || a.nVH != a.nKV)) return GL_ERR_SHAPE;
+    if (a.B > 65535 || a.splits > 65535) return GL_ERR_SHAPE;
+    const size_t stages = 16 * (size_t)AP_ROW + 2 * (size_t)AP_TILE + (a.v_in_k ? 0 : 2 * (size_t)AP_VTILE);
+    const size_t merge = 16 * (size_t)AP_ROW + (4 * 16 * (size_t)AP_VD + 4 * 16 * 2) * sizeof(float);
+    const size_t smem = stages > merge ? stages : merge;
+    if (smem > 227 * 1024) return GL_ERR_SMEM;
+    static size_t configured = 0;
+    if (smem > configured) {
+        if (cudaFuncSetAttribute(attn_rows_decode_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
+            cudaGetLastError();
+            return GL_ERR_SMEM;
+        }
+        configured = smem;
+    }
+    dim3 grid(a.nH / a.rows, a.B, a.splits);
+    return gl_launch(attn_rows_decode_tc_kernel, grid, dim3(AP_THREADS), smem, stream, 1, a) == 0 ? GL_OK : GL_ERR_LAUNCH;
+}
+
 GL_API int gl_attention_pairs_tc_dims() { return AP_HD * 1000 + AP_VD; }
 
 GL_API int gl_attention_pairs_tc(const PairsArgs* args, cudaStream_t stream) {

@@ -1340,6 +1340,28 @@ class _PairsArgs(Structure):
 
 
 USE_PAIRS_TC = True
+USE_ROWS_DECODE_TC = True      # one token a sequence, eight or more query heads on a key head: the heads as rows of a tensor-core product
+
+
+class _RowsDecodeArgs(Structure):
+    _fields_ = [("q", c_void_p), ("k_cache", c_void_p), ("v_cache", c_void_p), ("seq_qstart", c_void_p), ("seq_ctx", c_void_p),
+                ("pages", c_void_p), ("parts", c_void_p), ("ml", c_void_p),
+                ("B", c_int), ("nH", c_int), ("nKV", c_int), ("nVH", c_int), ("max_pages", c_int), ("window", c_int),
+                ("splits", c_int), ("pages_per_split", c_int), ("rows", c_int), ("v_in_k", c_int), ("score_scale", c_float)]
+
+
+def rows_decode_smem(head_dim: int, value_dim: int, values_in_keys: bool) -> int:
+    stages = 16 * (2 * head_dim + 16) + 2 * 64 * (2 * head_dim + 16) + (0 if values_in_keys else 2 * 64 * (2 * value_dim + 16))
+    return max(stages, 16 * (2 * head_dim + 16) + (4 * 16 * value_dim + 128) * 4)
+
+
+def rows_decode_splits(batch: int, runs: int, span_pages: int, device, smem: int) -> int:
+    """Ranges of pages a sequence's context is cut into for the kernel whose rows are query heads: enough blocks
+    (runs of heads x sequences x ranges) to fill the blocks an SM holds of it twice over, no range shorter than a page."""
+    pages = max(1, int(span_pages))
+    per_sm = max(1, min(4, (227 * 1024) // max(1, smem)))
+    want = max(1, (2 * per_sm * sm_count(device)) // max(1, batch * runs))
+    return max(1, min(pages, want, 64))
 
 
 def attention_mixed(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, ctx, pages: torch.Tensor,
@@ -1391,11 +1413,42 @@ def attention_mixed(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tenso
                        ctx.seq_qstart.data_ptr(), ctx.seq_qlen.data_ptr(), ctx.seq_ctx.data_ptr(), pages.data_ptr(),
                        T, ctx.n_seqs, num_heads, num_kv_heads, head_dim, value_dim, pages.shape[-1], window,
                        ctx.max_qlen, k_cache.shape[0], None, None, 0, 0, score_scale, softcap, _addr(slopes), _addr(sinks), nvh)
-    if (ctx.max_qlen == 1 and num_heads // num_kv_heads <= 8 and value_dim <= 128
-            and (num_kv_heads if mix is not None else (nvh or num_kv_heads) // num_kv_heads) <= 8):
+    group, share = num_heads // num_kv_heads, num_heads // (nvh or num_kv_heads)
+    rows = min(share, 16)
+    if (USE_ROWS_DECODE_TC and ctx.max_qlen == 1 and mix is None and softcap == 0.0 and slopes is None and not DEBUG_BOUNDS
+            and q.dtype == torch.bfloat16 and k_cache.dtype == torch.bfloat16 and head_dim % 16 == 0 and value_dim % 16 == 0
+            and head_dim <= 256 and value_dim <= 256 and group >= 8 and rows >= 4 and share % rows == 0
+            and rows_decode_smem(head_dim, value_dim, False) <= 227 * 1024):
+        # one token a sequence and many query heads on a key head: runs of heads that share a value head are the rows
+        # of a tensor-core product over the key head's pages; the ranges are put together by the mixing kernel
+        smem = rows_decode_smem(head_dim, value_dim, False)
+        span = max(1, -(-int(ctx.max_len) // PAGE))          # pages a token's keys can lie on
+        if window > 0:
+            span = min(span, -(-window // PAGE) + 1)
+        splits = rows_decode_splits(ctx.n_seqs, num_heads // rows, span, q.device, smem)
+        a.splits = splits
+        a.pages_per_split = -(-span // splits)
+        parts = empty((ctx.n_seqs, num_heads, 1, splits, value_dim), torch.float32, q.device)
+        ml = empty((ctx.n_seqs, num_heads, splits, 2), torch.float32, q.device)
+        a.parts, a.ml = parts.data_ptr(), ml.data_ptr()
+        r = _RowsDecodeArgs(q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), ctx.seq_qstart.data_ptr(),
+                            ctx.seq_ctx.data_ptr(), pages.data_ptr(), parts.data_ptr(), ml.data_ptr(), ctx.n_seqs, num_heads,
+                            num_kv_heads, nvh or num_kv_heads, pages.shape[-1], window, splits, a.pages_per_split, rows, 0,
+                            score_scale)
+        fn = _lib("attention_mixed_tc.cu", catalog.pair_dim_defines(head_dim, value_dim)).gl_attention_rows_decode_tc
+        _check(_launch(fn, byref(r), _stream()), "attention_rows_decode_tc")
+        _check(_launch(_lib("attention_mixed.cu").gl_head_mix_split, byref(a), c_int(dtype_code(q.dtype)), _stream()), "head_mix_split")
+        return out
+    if mix is not None:
+        by_key_head = group <= 8 and num_kv_heads <= 8
+    elif group <= 8:
+        by_key_head = group % min(share, group) == 0
+    else:                           # runs of eight query heads of a key head, whose value heads are whole within a run or span runs
+        by_key_head = group % 8 == 0 and (share % 8 == 0 if share >= 8 else 8 % share == 0)
+    if ctx.max_qlen == 1 and by_key_head and value_dim <= 128:
         # one token a sequence: the context in ranges of pages, a block each (sized for the step's longest
         # sequence; a captured step is sized for its bucket's longest), put together by the mixing kernel
-        splits = mixed_decode_splits(ctx.n_seqs, num_kv_heads, ctx.max_len, q.device)
+        splits = mixed_decode_splits(ctx.n_seqs, num_kv_heads * max(1, group // 8), ctx.max_len, q.device)
         a.splits = splits
         a.pages_per_split = -(-max(1, -(-int(ctx.max_len) // PAGE)) // splits)
         parts = empty((ctx.n_seqs, num_heads, n_val, splits, value_dim), torch.float32, q.device)

@@ -99,7 +99,7 @@ def latent_attention(h, w, pre, m, eps):
     share, a window, a sink per head in the denominator and a gate per head on the output."""
     T = h.shape[0]
     H, D, R, V, L = m["heads"], m["dim"], m["rot_dim"], m["vdim"], m["kv_rank"]
-    rot = {"dims": R, "base": m["rot"]["base"]}
+    rot = {"dims": R, "base": m["rot"]["base"]} if R else None
     cq = unit_rms(h @ w[pre + "dq"].T, eps) * w[pre + "dq.norm"]
     q = (cq @ w[pre + "uq"].T).view(T, H, D + R)
     q_flat, q_turn = q[..., :D], rotate_neighbours(q[..., D:], rot)

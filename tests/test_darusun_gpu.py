@@ -99,11 +99,53 @@ WIDE = dict(
          "mlp": {"kind": "moe", "expert": {"ff": 128}, "router": {"experts": 8, "top": 2}}},
     ])
 
+# more query heads than one block of the one-token kernel takes on a key head: sixteen (two runs of eight, value heads
+# that span a run and value heads inside a run) and twelve (no whole runs: the kernel by pairs)
+MANY = dict(
+    architecture="Darusun", vocab=200, width=64, norm={"eps": 1e-6}, residual_mult=0.6,
+    layers=[
+        {"type": "latent_attention",
+         "mixer": {"heads": 16, "dim": 8, "rot_dim": 8, "vdim": 8, "q_rank": 24, "kv_rank": 24, "scale": 0.3,
+                   "mask": {"size": 100}, "rot": {"dims": 8, "base": 1000.0}}, "mlp": None},
+        {"type": "attention",
+         "mixer": {"heads": 16, "kv_heads": 2, "dim": 16, "vdim": 8, "scale": 0.3, "rot": {"dims": 16, "base": 1000.0}},
+         "mlp": None},
+        {"type": "attention",
+         "mixer": {"heads": 16, "kv_heads": 8, "dim": 8, "vdim": 16, "scale": 0.3, "rot": {"dims": 4, "base": 1000.0}},
+         "mlp": None},
+        {"type": "attention",
+         "mixer": {"heads": 12, "kv_heads": 3, "dim": 8, "vdim": 8, "scale": 0.3, "rot": {"dims": 8, "base": 1000.0}},
+         "mlp": None},
+    ])
+
+# sizes the tensor-core kernel of one-token steps takes (key and value sizes in sixteens, eight or more query heads on
+# the key row): sixteen heads on a latent, runs of eight and of four heads that share a value head
+ROWS = dict(
+    architecture="Darusun", vocab=200, width=64, norm={"eps": 1e-6}, residual_mult=0.9,
+    layers=[
+        {"type": "latent_attention",
+         "mixer": {"heads": 16, "dim": 8, "rot_dim": 16, "vdim": 8, "q_rank": 24, "kv_rank": 48, "scale": 0.3,
+                   "mask": {"size": 100}, "rot": {"dims": 16, "base": 1000.0}}, "mlp": None},
+        {"type": "attention",
+         "mixer": {"heads": 16, "kv_heads": 2, "dim": 16, "vdim": 16, "scale": 0.3, "rot": {"dims": 16, "base": 1000.0}},
+         "mlp": None},
+        {"type": "attention",
+         "mixer": {"heads": 8, "kv_heads": 2, "dim": 32, "vdim": 32, "scale": 0.3, "rot": {"dims": 8, "base": 1000.0}},
+         "mlp": None},
+        {"type": "latent_attention",
+         "mixer": {"heads": 32, "dim": 16, "rot_dim": 0, "vdim": 8, "q_rank": 24, "kv_rank": 32, "scale": 0.3},
+         "mlp": None},
+    ])
+
 ALONE = [("talking_heads_with_shared_expert", dm.only(dm.ALPHA, 0)), ("latent_dense", dm.only(dm.ALPHA, 1)),
          ("talking_heads_bare", dm.only(dm.ALPHA, 2, mlp=False)), ("latent_top1", dm.only(dm.ALPHA, 3)),
          ("latent_small_rotation_long_window", dm.only(dm.BETA, 0)), ("talking_full_rotation_top3", dm.only(dm.BETA, 1)),
          ("talking_six_on_one_no_rotation", dm.only(dm.BETA, 2)), ("talking_odd_all_experts", dm.only(dm.GAMMA, 0)),
-         ("latent_one_head_window_three", dm.only(dm.GAMMA, 1)), ("latent_window_of_one", dm.only(dm.GAMMA, 2))]
+         ("latent_one_head_window_three", dm.only(dm.GAMMA, 1)), ("latent_window_of_one", dm.only(dm.GAMMA, 2)),
+         ("latent_sixteen_heads", dm.only(MANY, 0)), ("talking_sixteen_on_two", dm.only(MANY, 1)),
+         ("talking_sixteen_on_eight", dm.only(MANY, 2)), ("talking_twelve_on_three", dm.only(MANY, 3)), ("many_heads", MANY),
+         ("rows_latent_sixteen", dm.only(ROWS, 0)), ("rows_talking_runs_of_eight", dm.only(ROWS, 1)),
+         ("rows_talking_runs_of_four", dm.only(ROWS, 2)), ("rows_latent_no_rotation_no_window", dm.only(ROWS, 3)), ("rows", ROWS)]
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
@@ -111,7 +153,7 @@ ALONE = [("talking_heads_with_shared_expert", dm.only(dm.ALPHA, 0)), ("latent_de
 def test_each_mechanism_alone(name, cfg, dtype):
     """One layer of one kind: a whole prompt across a page's edge, then single tokens."""
     folder = folder_for(name, cfg, 11)
-    toks = tokens_for(cfg, 78, 1)
+    toks = tokens_for(cfg, 150 if name.startswith("rows") else 78, 1)
     m = load(folder, dtype)
     s = m.open_sequence()
     got = feed(m, s, toks, [70])
