@@ -34,7 +34,8 @@ RELEASED = -1        # in a sequence's list of pages: this one lay before the wi
 @dataclass
 class KVView:
     """What a mixer gets for its run: this entry's pages of keys and values
-    ([pages, kv_heads, PAGE, head_dim] and [pages, value_heads, PAGE, value_dim]), the group whose page table
+    ([pages, kv_heads, PAGE, head_dim] and [pages, value_heads, PAGE, value_dim]; where the values are the first
+    columns of the key rows, ``v`` is ``k``), the group whose page table
     (ctx.pages[group]) addresses them, and whether this run writes them."""
     group: int
     k: torch.Tensor
@@ -112,9 +113,9 @@ class SequenceCache:
                 r = g.req
                 g.keys = torch.empty((len(g.entries), self.n_pages, r.num_kv_heads, PAGE, r.head_dim),
                                      dtype=dtype, device=device)
-                g.values = torch.empty((len(g.entries), self.n_pages, r.value_heads or r.num_kv_heads, PAGE,
-                                        r.value_dim or r.head_dim),
-                                       dtype=dtype, device=device)
+                if not r.values_in_keys:
+                    g.values = torch.empty((len(g.entries), self.n_pages, r.value_heads or r.num_kv_heads, PAGE,
+                                            r.value_dim or r.head_dim), dtype=dtype, device=device)
         # per-slot bookkeeping
         self._length = [0] * self.max_slots
         self._pages: List[List[List[int]]] = [[[] for _ in self.groups] for _ in range(self.max_slots)]
@@ -130,7 +131,8 @@ class SequenceCache:
         """Key and value bytes one cached position occupies, all entries together."""
         es = torch.empty((), dtype=self.dtype).element_size()
         return sum(len(g.entries) * (g.req.num_kv_heads * g.req.head_dim
-                                     + (g.req.value_heads or g.req.num_kv_heads) * (g.req.value_dim or g.req.head_dim)) * es
+                                     + (0 if g.req.values_in_keys else
+                                        (g.req.value_heads or g.req.num_kv_heads) * (g.req.value_dim or g.req.head_dim))) * es
                    for g in self.groups)
 
     # -- views ------------------------------------------------------------
@@ -142,7 +144,8 @@ class SequenceCache:
             return tuple(self.view((entry, j), writes) for j in range(a))
         if kind == "kv":
             g = self.groups[a]
-            return KVView(group=a, k=g.keys[b], v=g.values[b], writes=writes)
+            # (a group whose values lie in its key rows hands out the keys twice)
+            return KVView(group=a, k=g.keys[b], v=g.values[b] if g.values is not None else g.keys[b], writes=writes)
         return StateView(rows=self._states[a], writes=writes)
 
     # -- sequences --------------------------------------------------------

@@ -39,7 +39,11 @@ struct MixedAttnArgs {
     const float* sinks;       // [nH] or null: e^(sinks[h]) joins the softmax's denominator of head h (no key, no value)
     int nVH;                  // heads of the value cache where they are more than the key heads (a multiple of nKV; 0: nKV):
                               // without a table, query head g then takes the values of head g / (nH / nVH)
+    int vs;                   // numbers between two positions' values of a head (0: vd).  A cache whose values are the
+                              // first vd columns of its key rows is read with v_cache = k_cache and vs = hd
 };
+
+__host__ __device__ __forceinline__ int am_value_stride(const MixedAttnArgs& a) { return a.vs > 0 ? a.vs : a.vd; }
 
 __host__ __device__ __forceinline__ int am_value_heads(const MixedAttnArgs& a) { return a.nVH > 0 ? a.nVH : a.nKV; }
 
@@ -108,15 +112,18 @@ attn_pairs_kernel(MixedAttnArgs a) {
     for (int page_i = lo_cta / GL_PAGE; page_i <= p_last / GL_PAGE; ++page_i) {
         const int page = gl_checked(pg[gl_checked(page_i, a.max_pages, GL_BAD_POSITION)], a.n_pages > 0 ? a.n_pages : 0x7fffffff, GL_BAD_PAGE);
         const TC* kp = (const TC*)a.k_cache + ((size_t)page * a.nKV + kh) * GL_PAGE * hd;
-        const TC* vp = (const TC*)a.v_cache + ((size_t)page * nvh + vh) * GL_PAGE * vd;
+        const int vs = am_value_stride(a);
+        const TC* vp = (const TC*)a.v_cache + ((size_t)page * nvh + vh) * GL_PAGE * vs;
         const int j0 = page_i * GL_PAGE;
         __syncthreads();
         for (int e = threadIdx.x; e < GL_PAGE * hd; e += blockDim.x) {
             const int r = e / hd, d = e - r * hd;
             Ks[r * ks + d] = j0 + r < total ? gl_load(kp + e) : 0.f;      // rows past the sequence were never written
         }
-        for (int e = threadIdx.x; e < GL_PAGE * vd; e += blockDim.x)
-            Vs[e] = j0 + e / vd < total ? gl_load(vp + e) : 0.f;
+        for (int e = threadIdx.x; e < GL_PAGE * vd; e += blockDim.x) {
+            const int r = e / vd;
+            Vs[e] = j0 + r < total ? gl_load(vp + (size_t)r * vs + (e - r * vd)) : 0.f;
+        }
         __syncthreads();
         if (!live) continue;
 #pragma unroll 1
@@ -195,7 +202,8 @@ attn_pairs_decode_kernel(MixedAttnArgs a) {
     for (int page_i = lo / GL_PAGE + warp; page_i <= p / GL_PAGE; page_i += AM_DWARPS) {
         const int page = gl_checked(pg[gl_checked(page_i, a.max_pages, GL_BAD_POSITION)], a.n_pages > 0 ? a.n_pages : 0x7fffffff, GL_BAD_PAGE);
         const TC* kp = (const TC*)a.k_cache + ((size_t)page * a.nKV + kh) * GL_PAGE * hd;
-        const TC* vp = (const TC*)a.v_cache + ((size_t)page * nvh + vh) * GL_PAGE * vd;
+        const int vs = am_value_stride(a);
+        const TC* vp = (const TC*)a.v_cache + ((size_t)page * nvh + vh) * GL_PAGE * vs;
         const int j0 = page_i * GL_PAGE;
 #pragma unroll 1
         for (int half = 0; half < GL_PAGE / 32; ++half) {
@@ -216,7 +224,7 @@ attn_pairs_decode_kernel(MixedAttnArgs a) {
             m = m_new;
 #pragma unroll
             for (int i = 0; i < NACC; ++i) acc[i] *= corr;
-            const TC* vr = vp + (size_t)half * 32 * vd;
+            const TC* vr = vp + (size_t)half * 32 * vs;
             // keys past p were never written, keys before lo may lie in a page that was given back
             const int kmin = max(0, lo - (j0 + half * 32)), kmax = min(32, p - (j0 + half * 32) + 1);
             for (int k = kmin; k < kmax; ++k) {
@@ -224,7 +232,7 @@ attn_pairs_decode_kernel(MixedAttnArgs a) {
 #pragma unroll
                 for (int i = 0; i < NACC; ++i) {
                     const int d = lane + 32 * i;
-                    if (d < vd) acc[i] = fmaf(pk, gl_load(vr + (size_t)k * vd + d), acc[i]);
+                    if (d < vd) acc[i] = fmaf(pk, gl_load(vr + (size_t)k * vs + d), acc[i]);
                 }
             }
         }
@@ -353,7 +361,8 @@ attn_group_decode_kernel(MixedAttnArgs a) {
         }
         __syncthreads();
         if (has_values) {
-            const TC* vp = (const TC*)a.v_cache + ((size_t)page * nvh + vh) * GL_PAGE * vd;
+            const int vs = am_value_stride(a);
+            const TC* vp = (const TC*)a.v_cache + ((size_t)page * nvh + vh) * GL_PAGE * vs;
 #pragma unroll
             for (int g = 0; g < GQ; ++g) {
                 if (g < gq) {
@@ -375,7 +384,7 @@ attn_group_decode_kernel(MixedAttnArgs a) {
 #pragma unroll
                     for (int i = 0; i < NACC; ++i) {
                         const int d = lane + 32 * i;
-                        v[kk][i] = (ok && d < vd) ? gl_load(vp + (size_t)(k0 + kk) * vd + d) : 0.f;
+                        v[kk][i] = (ok && d < vd) ? gl_load(vp + (size_t)(k0 + kk) * vs + d) : 0.f;
                     }
                 }
 #pragma unroll
@@ -565,6 +574,7 @@ GL_API int gl_attention_mixed(const MixedAttnArgs* args, int act_dtype, int cach
     if (a.B <= 0 || a.max_qlen <= 0 || a.T <= 0) return GL_OK;
     if (a.hd <= 0 || a.hd > 512 || a.vd <= 0 || a.vd > 256 || a.nH <= 0 || a.nKV <= 0 || a.nH % a.nKV) return GL_ERR_SHAPE;
     if (a.nVH < 0 || (a.nVH > 0 && (a.nVH % a.nKV || a.nH % a.nVH || (a.mix && a.nVH != a.nKV)))) return GL_ERR_SHAPE;
+    if (a.vs < 0 || (a.vs > 0 && a.vs < a.vd)) return GL_ERR_SHAPE;
     if (a.B > 65535 || a.nH * a.nKV > 65535) return GL_ERR_SHAPE;
     if (act_dtype == GL_F32 && cache_dtype == GL_F32) return dispatch_mixed<float, float>(a, stream);
     if (act_dtype == GL_BF16 && cache_dtype == GL_BF16) return dispatch_mixed<__nv_bfloat16, __nv_bfloat16>(a, stream);

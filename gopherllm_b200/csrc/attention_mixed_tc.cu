@@ -48,6 +48,8 @@ struct PairsArgs {
     const float* sinks;       // [nH] or null: e^(sinks[h]) joins the softmax's denominator of head h
     int nVH;                  // heads of the value cache where they are more than the key heads (0: nKV); without a
                               // table, query head h then takes the values of head h / (nH / nVH)
+    int vs;                   // numbers between two positions' values of a head (0: the value size); a cache whose values
+                              // are the first columns of its key rows is read with v_cache = k_cache and vs = the key size
 };
 
 __device__ __forceinline__ unsigned ap_smem(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
@@ -123,7 +125,8 @@ attn_pairs_tc_kernel(PairsArgs a) {
     const __nv_bfloat16* K = (const __nv_bfloat16*)a.k_cache;
     const __nv_bfloat16* V = (const __nv_bfloat16*)a.v_cache;
     const size_t head_off = (size_t)g * GL_PAGE * AP_HD, page_stride = (size_t)a.nKV * GL_PAGE * AP_HD;
-    const size_t vhead_off = (size_t)vh * GL_PAGE * AP_VD, vpage_stride = (size_t)nvh * GL_PAGE * AP_VD;
+    const size_t vs = a.vs > 0 ? (size_t)a.vs : (size_t)AP_VD;
+    const size_t vhead_off = (size_t)vh * GL_PAGE * vs, vpage_stride = (size_t)nvh * GL_PAGE * vs;
     const int total = ctx + qlen;
 
     // the query tile, then the first page
@@ -131,7 +134,7 @@ attn_pairs_tc_kernel(PairsArgs a) {
     {
         const int nv = min(GL_PAGE, total - page_begin * GL_PAGE);
         ap_load_rows<AP_HD>(sK[0], K + (size_t)pg[page_begin] * page_stride + head_off, AP_HD, nv);
-        ap_load_rows<AP_VD>(sV[0], V + (size_t)pg[page_begin] * vpage_stride + vhead_off, AP_VD, nv);
+        ap_load_rows<AP_VD>(sV[0], V + (size_t)pg[page_begin] * vpage_stride + vhead_off, vs, nv);
     }
     ap_commit();
 
@@ -156,7 +159,7 @@ attn_pairs_tc_kernel(PairsArgs a) {
         if (p + 1 < page_end) {
             const int nv = min(GL_PAGE, total - (p + 1) * GL_PAGE);
             ap_load_rows<AP_HD>(sK[st ^ 1], K + (size_t)pg[p + 1] * page_stride + head_off, AP_HD, nv);
-            ap_load_rows<AP_VD>(sV[st ^ 1], V + (size_t)pg[p + 1] * vpage_stride + vhead_off, AP_VD, nv);
+            ap_load_rows<AP_VD>(sV[st ^ 1], V + (size_t)pg[p + 1] * vpage_stride + vhead_off, vs, nv);
         }
         ap_commit();
         ap_wait<1>();
@@ -548,6 +551,7 @@ GL_API int gl_attention_pairs_tc(const PairsArgs* args, cudaStream_t stream) {
     if (a.B <= 0 || a.max_qlen <= 0) return GL_OK;
     if (a.nH <= 0 || a.nKV <= 0 || a.nH % a.nKV || (a.nVal != 1 && a.nVal != a.nKV)) return GL_ERR_SHAPE;
     if (a.nVH < 0 || (a.nVH > 0 && (a.nH % a.nVH || (a.nVal != 1 && a.nVH != a.nKV)))) return GL_ERR_SHAPE;
+    if (a.vs < 0 || (a.vs > 0 && (a.vs < AP_VD || a.vs % 8))) return GL_ERR_SHAPE;
     if (a.B > 65535 || a.nH * a.nVal > 65535) return GL_ERR_SHAPE;
     const size_t smem = 3 * (size_t)AP_TILE + 2 * (size_t)AP_VTILE;
     static bool configured = false;

@@ -9,7 +9,8 @@
 //
 //   gl_latent_prepare   a token's down projections [query latent | c | rotated key part | ...]: both latents
 //                       RMS-normed with a weight, the key part rotated; the query latent written out, the row
-//                       [c | key part] and the values c written to the token's place in the cache.
+//                       [c | key part] written to the token's place in the cache (the values are its first columns;
+//                       a cache that keeps values of its own gets c once more).
 //   gl_head_linear      out[t, h, :] = W_h x[t, h, :] per head (strided rows on both sides), optionally followed by
 //                       a rotated copy of the columns behind x[t, h, :K] (the query's rotated part) and optionally
 //                       times sigmoid(gate[t, h]) (an output gate per head).
@@ -21,7 +22,7 @@ struct LatentPrepareArgs {
     const void* proj;         // [T, ld] activation type: query latent (q_rank), c (kv_rank), key part (rot), then others
     void* cq_out;             // [T, q_rank] activation type: the normed query latent
     void* k_cache;            // [pages, 1, GL_PAGE, kv_rank + rot] cache type
-    void* v_cache;            // [pages, 1, GL_PAGE, kv_rank] cache type
+    void* v_cache;            // [pages, 1, GL_PAGE, kv_rank] cache type, or null: the values are read from the key rows
     const float* cosv;        // [T, rot / 2] or null
     const float* sinv;
     const float* q_gamma;     // [q_rank]
@@ -73,7 +74,7 @@ latent_prepare_kernel(LatentPrepareArgs a) {
     for (int i = threadIdx.x; i < a.kv_rank; i += blockDim.x) {
         const float y = c[i] * inv_k * a.kv_gamma[i];
         gl_store(kr + i, y);
-        gl_store(vr + i, y);
+        if (a.v_cache) gl_store(vr + i, y);
     }
     const float* kp = c + a.kv_rank;
     const int half = a.rot / 2;

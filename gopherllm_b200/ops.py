@@ -1313,7 +1313,8 @@ class _MixedAttnArgs(Structure):
                 ("T", c_int), ("B", c_int), ("nH", c_int), ("nKV", c_int), ("hd", c_int), ("vd", c_int),
                 ("max_pages", c_int), ("window", c_int), ("max_qlen", c_int), ("n_pages", c_int),
                 ("parts", c_void_p), ("ml", c_void_p), ("splits", c_int), ("pages_per_split", c_int),
-                ("score_scale", c_float), ("softcap", c_float), ("slopes", c_void_p), ("sinks", c_void_p), ("nVH", c_int)]
+                ("score_scale", c_float), ("softcap", c_float), ("slopes", c_void_p), ("sinks", c_void_p), ("nVH", c_int),
+                ("vs", c_int)]
 
 
 # A block of the one-token kernel walks its pages one after the other and waits for each: what hides the trips to
@@ -1336,7 +1337,7 @@ class _PairsArgs(Structure):
                 ("seq_qstart", c_void_p), ("seq_qlen", c_void_p), ("seq_ctx", c_void_p), ("pages", c_void_p),
                 ("B", c_int), ("nH", c_int), ("nKV", c_int), ("nVal", c_int), ("max_pages", c_int), ("window", c_int),
                 ("max_qlen", c_int), ("score_scale", c_float), ("softcap", c_float), ("slopes", c_void_p),
-                ("out", c_void_p), ("sinks", c_void_p), ("nVH", c_int)]
+                ("out", c_void_p), ("sinks", c_void_p), ("nVH", c_int), ("vs", c_int)]
 
 
 USE_PAIRS_TC = True
@@ -1368,7 +1369,7 @@ def attention_mixed(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tenso
                     num_heads: int, num_kv_heads: int, head_dim: int, value_dim: int,
                     mix: Optional[torch.Tensor] = None, window: int = 0, score_scale: float = 1.0,
                     softcap: float = 0.0, slopes: Optional[torch.Tensor] = None,
-                    sinks: Optional[torch.Tensor] = None, value_heads: int = 0) -> torch.Tensor:
+                    sinks: Optional[torch.Tensor] = None, value_heads: int = 0, values_in_keys: bool = False) -> torch.Tensor:
     """Causal softmax attention of scaled queries [T, nH*hd] over the paged cache; with ``mix`` [nH, nH]
     head h applies sum_g mix[h, g] * (head g's softmax weights) to the values of its own key/value
     head.  A score is (q . k) * score_scale, then softcap * tanh(score / softcap) when softcap > 0, then
@@ -1376,7 +1377,8 @@ def attention_mixed(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tenso
     [nH] float32 the denominator of head h's softmax also holds exp(sinks[h]), once, with no key and no value.
     ``value_heads`` > 0: the value cache has that many heads (a multiple of the key heads), and without a table
     query head h takes the values of head h / (nH / value_heads): many query heads on one wide key head, each
-    with one of several value heads.
+    with one of several value heads.  ``values_in_keys``: a position's values are the first ``value_dim`` numbers of its
+    key row (``v_cache`` is the key cache).
     Returns [T, nH*vd] in q's type.  Prompts in bfloat16 with key and value sizes that are
     multiples of 16 compute the (query head, value head) pairs on the tensor cores (a library per pair
     of sizes); everything else runs the 32-bit kernels."""
@@ -1393,7 +1395,13 @@ def attention_mixed(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tenso
     nvh = int(value_heads)
     if nvh and (nvh % num_kv_heads or num_heads % nvh or (mix is not None and nvh != num_kv_heads)):
         raise KernelError(f"attention_mixed: {nvh} value heads do not fit {num_heads} query heads on {num_kv_heads} key heads")
-    if tuple(v_cache.shape[1:]) != (nvh or num_kv_heads, PAGE, value_dim) or tuple(k_cache.shape[1:]) != (num_kv_heads, PAGE, head_dim):
+    vs = 0
+    if values_in_keys:
+        if mix is not None or nvh not in (0, num_kv_heads) or value_dim > head_dim:
+            raise KernelError("attention_mixed: values inside the key rows come one row of values a key head, no longer than it")
+        v_cache, vs = k_cache, head_dim
+    if (tuple(v_cache.shape[1:]) != (nvh or num_kv_heads, PAGE, vs or value_dim)
+            or tuple(k_cache.shape[1:]) != (num_kv_heads, PAGE, head_dim)):
         raise KernelError(f"attention_mixed: cache pages do not fit: keys {tuple(k_cache.shape)}, values {tuple(v_cache.shape)}")
     out = empty((T, num_heads * value_dim), q.dtype, q.device)
     pairs_tc = (USE_PAIRS_TC and ctx.max_qlen > 1 and q.dtype == torch.bfloat16 and k_cache.dtype == torch.bfloat16
@@ -1404,7 +1412,7 @@ def attention_mixed(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tenso
         p = _PairsArgs(q.data_ptr(), None, k_cache.data_ptr(), v_cache.data_ptr(),
                        ctx.seq_qstart.data_ptr(), ctx.seq_qlen.data_ptr(), ctx.seq_ctx.data_ptr(), pages.data_ptr(),
                        ctx.n_seqs, num_heads, num_kv_heads, 1, pages.shape[-1], window, ctx.max_qlen,
-                       score_scale, softcap, _addr(slopes), out.data_ptr(), _addr(sinks), nvh)
+                       score_scale, softcap, _addr(slopes), out.data_ptr(), _addr(sinks), nvh, vs)
         fn = _lib("attention_mixed_tc.cu", catalog.pair_dim_defines(head_dim, value_dim)).gl_attention_pairs_tc
         _check(_launch(fn, byref(p), _stream()), "attention_pairs_tc")
         return out
@@ -1412,16 +1420,16 @@ def attention_mixed(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tenso
     a = _MixedAttnArgs(q.data_ptr(), pairs.data_ptr(), out.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), _addr(mix),
                        ctx.seq_qstart.data_ptr(), ctx.seq_qlen.data_ptr(), ctx.seq_ctx.data_ptr(), pages.data_ptr(),
                        T, ctx.n_seqs, num_heads, num_kv_heads, head_dim, value_dim, pages.shape[-1], window,
-                       ctx.max_qlen, k_cache.shape[0], None, None, 0, 0, score_scale, softcap, _addr(slopes), _addr(sinks), nvh)
+                       ctx.max_qlen, k_cache.shape[0], None, None, 0, 0, score_scale, softcap, _addr(slopes), _addr(sinks), nvh, vs)
     group, share = num_heads // num_kv_heads, num_heads // (nvh or num_kv_heads)
     rows = min(share, 16)
     if (USE_ROWS_DECODE_TC and ctx.max_qlen == 1 and mix is None and softcap == 0.0 and slopes is None and not DEBUG_BOUNDS
             and q.dtype == torch.bfloat16 and k_cache.dtype == torch.bfloat16 and head_dim % 16 == 0 and value_dim % 16 == 0
             and head_dim <= 256 and value_dim <= 256 and group >= 8 and rows >= 4 and share % rows == 0
-            and rows_decode_smem(head_dim, value_dim, False) <= 227 * 1024):
+            and rows_decode_smem(head_dim, value_dim, values_in_keys) <= 227 * 1024):
         # one token a sequence and many query heads on a key head: runs of heads that share a value head are the rows
         # of a tensor-core product over the key head's pages; the ranges are put together by the mixing kernel
-        smem = rows_decode_smem(head_dim, value_dim, False)
+        smem = rows_decode_smem(head_dim, value_dim, values_in_keys)
         span = max(1, -(-int(ctx.max_len) // PAGE))          # pages a token's keys can lie on
         if window > 0:
             span = min(span, -(-window // PAGE) + 1)
@@ -1433,8 +1441,8 @@ def attention_mixed(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tenso
         a.parts, a.ml = parts.data_ptr(), ml.data_ptr()
         r = _RowsDecodeArgs(q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), ctx.seq_qstart.data_ptr(),
                             ctx.seq_ctx.data_ptr(), pages.data_ptr(), parts.data_ptr(), ml.data_ptr(), ctx.n_seqs, num_heads,
-                            num_kv_heads, nvh or num_kv_heads, pages.shape[-1], window, splits, a.pages_per_split, rows, 0,
-                            score_scale)
+                            num_kv_heads, nvh or num_kv_heads, pages.shape[-1], window, splits, a.pages_per_split, rows,
+                            1 if values_in_keys else 0, score_scale)
         fn = _lib("attention_mixed_tc.cu", catalog.pair_dim_defines(head_dim, value_dim)).gl_attention_rows_decode_tc
         _check(_launch(fn, byref(r), _stream()), "attention_rows_decode_tc")
         _check(_launch(_lib("attention_mixed.cu").gl_head_mix_split, byref(a), c_int(dtype_code(q.dtype)), _stream()), "head_mix_split")
@@ -1459,7 +1467,7 @@ def attention_mixed(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tenso
         p = _PairsArgs(q.data_ptr(), pairs.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(),
                        ctx.seq_qstart.data_ptr(), ctx.seq_qlen.data_ptr(), ctx.seq_ctx.data_ptr(), pages.data_ptr(),
                        ctx.n_seqs, num_heads, num_kv_heads, n_val, pages.shape[-1], window, ctx.max_qlen,
-                       score_scale, softcap, _addr(slopes), None, _addr(sinks), nvh)
+                       score_scale, softcap, _addr(slopes), None, _addr(sinks), nvh, vs)
         fn = _lib("attention_mixed_tc.cu", catalog.pair_dim_defines(head_dim, value_dim)).gl_attention_pairs_tc
         _check(_launch(fn, byref(p), _stream()), "attention_pairs_tc")
         _check(_launch(lib.gl_head_mix, byref(a), c_int(dtype_code(q.dtype)), _stream()), "head_mix")
@@ -1516,13 +1524,16 @@ def latent_prepare(proj: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Ten
                    write_kv: bool = True) -> torch.Tensor:
     """A token's down projections proj [T, ld] = [query latent (q_rank) | c (kv_rank) | key part (rot) | ...]: both
     latents RMS-normed with their weights (32-bit), the key part rotated by the token's angles; the row [c | key part]
-    goes to the token's place in k_cache [pages, 1, PAGE, kv_rank + rot], c to v_cache [pages, 1, PAGE, kv_rank].
+    goes to the token's place in k_cache [pages, 1, PAGE, kv_rank + rot], c to v_cache [pages, 1, PAGE, kv_rank]
+    (``v_cache`` None or the key cache itself: the values are read from the key rows, nothing more is written).
     Returns the normed query latent [T, q_rank]."""
     _need(proj, "proj")
     T, ld = proj.shape
     if ld < q_rank + kv_rank + rot:
         raise KernelError("latent_prepare: the projection's rows are too short")
-    if tuple(k_cache.shape[1:]) != (1, PAGE, kv_rank + rot) or tuple(v_cache.shape[1:]) != (1, PAGE, kv_rank):
+    if v_cache is not None and v_cache.data_ptr() == k_cache.data_ptr():
+        v_cache = None
+    if tuple(k_cache.shape[1:]) != (1, PAGE, kv_rank + rot) or (v_cache is not None and tuple(v_cache.shape[1:]) != (1, PAGE, kv_rank)):
         raise KernelError(f"cache pages do not fit: keys {tuple(k_cache.shape)}, values {tuple(v_cache.shape)}")
     _need(q_gamma, "q_gamma", torch.float32, (q_rank,))
     _need(kv_gamma, "kv_gamma", torch.float32, (kv_rank,))
@@ -1530,7 +1541,7 @@ def latent_prepare(proj: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Ten
         _need(cos, "cos", torch.float32, (T, rot // 2))
         _need(sin, "sin", torch.float32, (T, rot // 2))
     cq = empty((T, q_rank), proj.dtype, proj.device)
-    a = _LatentPrepareArgs(proj.data_ptr(), cq.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), _addr(cos), _addr(sin),
+    a = _LatentPrepareArgs(proj.data_ptr(), cq.data_ptr(), k_cache.data_ptr(), _addr(v_cache), _addr(cos), _addr(sin),
                            q_gamma.data_ptr(), kv_gamma.data_ptr(), ctx.tok_seq.data_ptr(), ctx.tok_pos.data_ptr(),
                            pages.data_ptr(), T, ld, q_rank, kv_rank, rot, pages.shape[-1], k_cache.shape[0],
                            1 if interleaved else 0, 1 if write_kv else 0, eps)

@@ -314,7 +314,7 @@ class LatentAttention(Mixer):
     and sink as in the other mixers; option ``gate``: head h's output times sigmoid(w_g,h . x); output projection.
 
     Keys and values are never built.  (W_uk,h^T q_h) . c = q_h . (W_uk,h c), and sum_j p_j W_uv,h c_j =
-    W_uv,h sum_j p_j c_j, so the cache holds the row [c | k_r] per position (and c once more as the values),
+    W_uv,h sum_j p_j c_j, so the cache holds the row [c | k_r] per position and nothing else (the values are its first columns),
     every query head becomes a row [W_uk,h^T q_h | its rotated part] of kv_rank + rot numbers, attention runs as
     ``num_heads`` query heads on ONE key head with values of size kv_rank, and W_uv,h is applied to a head's result.
     The three down projections (query latent, [c' | k_r], gates) are one product; the per-head products are
@@ -377,7 +377,7 @@ class LatentAttention(Mixer):
         self.sinks = t.get("sink")
 
     def cache_request(self):
-        return KVRequest(1, self.kv_rank + self.rot, self.spec.window, value_dim=self.kv_rank)
+        return KVRequest(1, self.kv_rank + self.rot, self.spec.window, value_dim=self.kv_rank, values_in_keys=True)
 
     def products(self):
         return [("down", self.w_down, None, None), ("uq", self.w_uq, None, None), ("o", self.w_out, None, None)]
@@ -397,7 +397,7 @@ class LatentAttention(Mixer):
         wide = ops.head_linear(q, self.w_uk_t, s.head_dim + self.rot, tail=self.rot, cos=cos, sin=sin,
                                interleaved=s.position.interleaved)
         mixed = ops.attention_mixed(wide, cache.k, cache.v, ctx, pages, H, 1, self.kv_rank + self.rot, self.kv_rank,
-                                    window=s.window, score_scale=self.score_scale, sinks=self.sinks)
+                                    window=s.window, score_scale=self.score_scale, sinks=self.sinks, values_in_keys=True)
         o = ops.head_linear(mixed, self.w_uv, self.kv_rank, gate=proj if self.gate else None,
                             gate_off=self.q_rank + self.kv_rank + self.rot)
         return o, self.w_out, None

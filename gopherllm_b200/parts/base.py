@@ -43,6 +43,7 @@ class KVRequest:
     window: int = 0
     value_dim: int = 0        # size of a head's values where it differs from head_dim (0: the same)
     value_heads: int = 0      # rows of values per position where they differ from the rows of keys (0: the same)
+    values_in_keys: bool = False   # a position's values are the first value_dim numbers of its key rows: nothing more is kept
 
 
 @dataclass(frozen=True)

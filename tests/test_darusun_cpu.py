@@ -67,14 +67,16 @@ def test_layers_that_read_another_layers_keys():
     reqs = model.cache_requests()
     # the latent: one row of kv_rank + rot_dim numbers, values of kv_rank, a window; three key heads side by side with
     # three rows of values; six heads on one key head
-    assert reqs[0] == KVRequest(1, 68, 130, value_dim=64)
+    assert reqs[0] == KVRequest(1, 68, 130, value_dim=64, values_in_keys=True)
     assert reqs[1] == KVRequest(1, 96, 0, value_dim=16, value_heads=3)
     assert reqs[2] == KVRequest(1, 16, 0)
     assert len(reqs) == 3          # the layers that read layer 1's keys keep nothing of their own
     cache = SequenceCache(reqs, max_tokens=256, max_positions=256, dtype=torch.float32, device="cpu", max_slots=2)
     kv = cache.view(1, writes=False)
     assert isinstance(kv, KVView) and tuple(kv.k.shape[1:]) == (1, 64, 96) and tuple(kv.v.shape[1:]) == (3, 64, 16)
-    assert cache.bytes_per_position() == 4 * ((68 + 64) + (96 + 48) + (16 + 16))
+    assert cache.bytes_per_position() == 4 * (68 + (96 + 48) + (16 + 16))
+    latent = cache.view(0)
+    assert latent.v.data_ptr() == latent.k.data_ptr() and tuple(latent.k.shape[1:]) == (1, 64, 68)
 
 
 def _with(cfg, path, value):
