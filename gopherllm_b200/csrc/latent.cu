@@ -14,8 +14,9 @@
 //   gl_head_linear      out[t, h, :] = W_h x[t, h, :] per head (strided rows on both sides), optionally followed by
 //                       a rotated copy of the columns behind x[t, h, :K] (the query's rotated part) and optionally
 //                       times sigmoid(gate[t, h]) (an output gate per head).
-// Norms, rotation, gates and all sums are 32-bit; one block a token in the first kernel, tiles of 64 x 64 with sums
-// over k in ascending order in the second.
+// Norms, rotation, gates and all sums are 32-bit; one block a token in the first kernel, tiles of 64 x 64 in the
+// second: on the CUDA cores with sums over k in ascending order (the 32-bit path, and sizes the other form does not
+// take), on the tensor cores for bfloat16 in whole 16-byte pieces.
 #include "common.cuh"
 
 struct LatentPrepareArgs {
@@ -210,6 +211,108 @@ head_linear_kernel(HeadLinearArgs g) {
     }
 }
 
+// The same product on the tensor cores for bfloat16 operands in whole 16-byte pieces: a block takes 64 tokens x 64
+// outputs of a head, each of its 4 warps 16 tokens; K passes through shared memory 64 at a time (padded rows, so
+// that the eight rows of an ldmatrix fall on different banks); mma.sync.m16n8k16 with 32-bit sums; the gate and the
+// rounding in the epilogue.
+#define HT_BK 64
+#define HT_ROW (HT_BK * 2 + 16)
+
+__device__ __forceinline__ void ht_ldm4(unsigned addr, unsigned& r0, unsigned& r1, unsigned& r2, unsigned& r3) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ void ht_mma(float (&d)[4], const unsigned (&a)[4], unsigned b0, unsigned b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+__global__ void __launch_bounds__(128)
+head_linear_tc_kernel(HeadLinearArgs g) {
+    __shared__ __align__(16) unsigned char sA[64 * HT_ROW];
+    __shared__ __align__(16) unsigned char sW[64 * HT_ROW];
+    gl_grid_launch_dependents();
+    gl_grid_wait();
+    const int h = blockIdx.z;
+    const __nv_bfloat16* X = (const __nv_bfloat16*)g.x + (size_t)h * g.x_head + g.x_off;
+    const __nv_bfloat16* W = (const __nv_bfloat16*)g.w + (size_t)h * g.N * g.K;
+    __nv_bfloat16* O = (__nv_bfloat16*)g.out + (size_t)h * g.o_head + g.o_off;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, grp = lane >> 2, t = lane & 3;
+    const int m0 = blockIdx.y * 64, n0 = blockIdx.x * 64;
+    if (blockIdx.x == 0 && g.tail > 0) {
+        const int half = g.tail / 2;
+        if (g.cosv) {
+            for (int e = tid; e < 64 * half; e += 128) {
+                const int r = e / half, i = e - r * half, m = m0 + r;
+                if (m >= g.T) break;
+                const int i0 = g.interleaved ? 2 * i : i, i1 = g.interleaved ? 2 * i + 1 : i + half;
+                const __nv_bfloat16* src = X + (size_t)m * g.x_row + g.K;
+                const float c = g.cosv[(size_t)m * half + i], s = g.sinv[(size_t)m * half + i];
+                const float u = gl_load(src + i0), x = gl_load(src + i1);
+                gl_store(O + (size_t)m * g.o_row + g.N + i0, u * c - x * s);
+                gl_store(O + (size_t)m * g.o_row + g.N + i1, x * c + u * s);
+            }
+        } else {
+            for (int e = tid; e < 64 * g.tail; e += 128) {
+                const int r = e / g.tail, i = e - r * g.tail, m = m0 + r;
+                if (m >= g.T) break;
+                O[(size_t)m * g.o_row + g.N + i] = X[(size_t)m * g.x_row + g.K + i];
+            }
+        }
+    }
+    float acc[8][4];
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) acc[j][e] = 0.f;
+    const unsigned a_base = (unsigned)__cvta_generic_to_shared(sA), w_base = (unsigned)__cvta_generic_to_shared(sW);
+    for (int k0 = 0; k0 < g.K; k0 += HT_BK) {
+        const int kc = min(HT_BK, g.K - k0);
+        for (int i = tid; i < 64 * 8; i += 128) {
+            const int r = i >> 3, c = i & 7;
+            uint4 va = make_uint4(0, 0, 0, 0), vw = make_uint4(0, 0, 0, 0);
+            if (c * 8 < kc) {
+                if (m0 + r < g.T) va = *(const uint4*)(X + (size_t)(m0 + r) * g.x_row + k0 + c * 8);
+                if (n0 + r < g.N) vw = *(const uint4*)(W + (size_t)(n0 + r) * g.K + k0 + c * 8);
+            }
+            *(uint4*)(sA + r * HT_ROW + c * 16) = va;
+            *(uint4*)(sW + r * HT_ROW + c * 16) = vw;
+        }
+        __syncthreads();
+        for (int kk = 0; kk < kc / 16; ++kk) {
+            unsigned af[4];
+            ht_ldm4(a_base + (warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * HT_ROW + (kk * 2 + (lane >> 4)) * 16,
+                    af[0], af[1], af[2], af[3]);
+#pragma unroll
+            for (int j = 0; j < 8; j += 2) {
+                unsigned b0, b1, b2, b3;
+                ht_ldm4(w_base + (j * 8 + ((lane >> 4) & 1) * 8 + (lane & 7)) * HT_ROW + (kk * 2 + ((lane >> 3) & 1)) * 16,
+                        b0, b1, b2, b3);
+                ht_mma(acc[j], af, b0, b1);
+                ht_mma(acc[j + 1], af, b2, b3);
+            }
+        }
+        __syncthreads();
+    }
+    const int r_lo = m0 + warp * 16 + grp, r_hi = r_lo + 8;
+    float mul_lo = 1.0f, mul_hi = 1.0f;
+    if (g.gate) {
+        const __nv_bfloat16* G = (const __nv_bfloat16*)g.gate;
+        if (r_lo < g.T) mul_lo = 1.0f / (1.0f + expf(-gl_load(G + (size_t)r_lo * g.g_row + g.g_off + h)));
+        if (r_hi < g.T) mul_hi = 1.0f / (1.0f + expf(-gl_load(G + (size_t)r_hi * g.g_row + g.g_off + h)));
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        const int n = n0 + j * 8 + 2 * t;
+        if (n >= g.N) continue;
+        if (r_lo < g.T)
+            *(__nv_bfloat162*)(O + (size_t)r_lo * g.o_row + n) = __floats2bfloat162_rn(acc[j][0] * mul_lo, acc[j][1] * mul_lo);
+        if (r_hi < g.T)
+            *(__nv_bfloat162*)(O + (size_t)r_hi * g.o_row + n) = __floats2bfloat162_rn(acc[j][2] * mul_hi, acc[j][3] * mul_hi);
+    }
+}
+
 GL_API int gl_head_linear(const HeadLinearArgs* args, int act_dtype, int w_dtype, cudaStream_t stream) {
     const HeadLinearArgs& g = *args;
     if (g.T <= 0 || g.H <= 0) return GL_OK;
@@ -217,6 +320,10 @@ GL_API int gl_head_linear(const HeadLinearArgs* args, int act_dtype, int w_dtype
     const dim3 grid((g.N + HL_BN - 1) / HL_BN, (g.T + HL_BM - 1) / HL_BM, g.H);
     if (grid.y > 65535) return GL_ERR_SHAPE;
     int rc;
+    if (act_dtype == GL_BF16 && w_dtype == GL_BF16 && g.K % 16 == 0 && g.N % 8 == 0 && g.x_row % 8 == 0 && g.x_head % 8 == 0 &&
+        g.x_off % 8 == 0 && g.o_row % 2 == 0 && g.o_head % 2 == 0 && g.o_off % 2 == 0 &&
+        !(((uintptr_t)g.x | (uintptr_t)g.w) & 15) && !((uintptr_t)g.out & 3))
+        return gl_launch(head_linear_tc_kernel, grid, dim3(128), 0, stream, 1, g) == 0 ? GL_OK : GL_ERR_LAUNCH;
     if (act_dtype == GL_F32 && w_dtype == GL_F32) rc = gl_launch(head_linear_kernel<float, float>, grid, dim3(256), 0, stream, 1, g);
     else if (act_dtype == GL_BF16 && w_dtype == GL_BF16)
         rc = gl_launch(head_linear_kernel<__nv_bfloat16, __nv_bfloat16>, grid, dim3(256), 0, stream, 1, g);

@@ -339,13 +339,31 @@ qkv_rownorm_cache_kernel(QkvRowNormArgs a) {
     if (a.temp_every > 0.f)
         q_mul *= 1.0f + a.temp_coef * logf((float)floor((double)(pos + 1) / (double)a.temp_every) + 1.0f);
     if (a.talk) {
+        // a thread a column (key head c, dim d) of the wide rows: the column's query heads' values stay in registers
+        // while the heads of the result are walked; the table's entries are the same for all threads of a step
         const int wide = a.nKV * a.hd, per = a.nH / a.nKV;
         TA* qo = (TA*)a.q_out + (size_t)t * a.nH * wide;
-        for (int i = threadIdx.x; i < a.nH * wide; i += blockDim.x) {
-            const int h = i / wide, r = i - h * wide, c = r / a.hd, d = r - c * a.hd;
-            float y = 0.f;
-            for (int g = c * per; g < (c + 1) * per; ++g) y = fmaf(a.talk[h * a.nH + g], v[(size_t)g * a.hd + d], y);
-            gl_store(qo + i, y * q_mul);
+        for (int r = threadIdx.x; r < wide; r += blockDim.x) {
+            const int c = r / a.hd, d = r - c * a.hd;
+            if (per <= 8) {
+                float qg[8];
+#pragma unroll
+                for (int g = 0; g < 8; ++g) qg[g] = g < per ? v[(size_t)(c * per + g) * a.hd + d] * q_mul : 0.f;
+                for (int h = 0; h < a.nH; ++h) {
+                    const float* row = a.talk + (size_t)h * a.nH + c * per;
+                    float y = 0.f;
+#pragma unroll
+                    for (int g = 0; g < 8; ++g)
+                        if (g < per) y = fmaf(row[g], qg[g], y);
+                    gl_store(qo + (size_t)h * wide + r, y);
+                }
+            } else {
+                for (int h = 0; h < a.nH; ++h) {
+                    float y = 0.f;
+                    for (int g = c * per; g < (c + 1) * per; ++g) y = fmaf(a.talk[h * a.nH + g], v[(size_t)g * a.hd + d], y);
+                    gl_store(qo + (size_t)h * wide + r, y * q_mul);
+                }
+            }
         }
     } else {
         TA* qo = (TA*)a.q_out + (size_t)t * nq;

@@ -480,8 +480,32 @@ xielu_kernel(TA* x, long long n, float up, float down) {
     }
 }
 
+// bfloat16 in whole 16-byte units: eight numbers a thread
+__global__ void __launch_bounds__(256)
+xielu_bf16x8_kernel(uint4* x, long long n8, float up, float down) {
+    gl_grid_launch_dependents();
+    gl_grid_wait();
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n8; i += (long long)gridDim.x * blockDim.x) {
+        uint4 raw = x[i];
+        __nv_bfloat162* p2 = (__nv_bfloat162*)&raw;
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const float2 z = __bfloat1622float2(p2[e]);
+            const float y0 = z.x > 0.f ? fmaf(up * z.x, z.x, 0.5f * z.x) : fmaf(down, expm1f(z.x) - z.x, 0.5f * z.x);
+            const float y1 = z.y > 0.f ? fmaf(up * z.y, z.y, 0.5f * z.y) : fmaf(down, expm1f(z.y) - z.y, 0.5f * z.y);
+            p2[e] = __floats2bfloat162_rn(y0, y1);
+        }
+        x[i] = raw;
+    }
+}
+
 GL_API int gl_xielu(void* x, long long n, float up, float down, int act_dtype, cudaStream_t stream) {
     if (n <= 0) return GL_OK;
+    if (act_dtype == GL_BF16 && n % 8 == 0 && !((uintptr_t)x & 15)) {
+        const long long n8 = n / 8, want8 = (n8 + 255) / 256;
+        return gl_launch(xielu_bf16x8_kernel, dim3((unsigned)(want8 > 16384 ? 16384 : want8)), dim3(256), 0, stream, 1, (uint4*)x, n8,
+                         up, down);
+    }
     const long long want = (n + 255) / 256;
     const dim3 grid((unsigned)(want > 8192 ? 8192 : want));
     if (act_dtype == GL_F32) return gl_launch(xielu_kernel<float>, grid, dim3(256), 0, stream, 1, (float*)x, n, up, down);

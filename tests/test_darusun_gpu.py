@@ -469,22 +469,24 @@ def test_kernels_of_the_design_alone():
     from gopherllm_b200 import ops
     dev = torch.device("cuda:0")
     g = torch.Generator().manual_seed(5)
-    T, H, N, K, tail = 70, 3, 20, 12, 6
-    x = torch.randn(T, H * (K + tail), generator=g)
-    w = torch.randn(H, N, K, generator=g)
-    ang = torch.randn(T, tail // 2, generator=g)
-    gate = torch.randn(T, 5 + H, generator=g)
-    for dtype, tol in ((torch.float32, 1e-5), (torch.bfloat16, 3e-2)):
-        xd, wd, gd = x.to(dev, dtype), w.to(dev, dtype), gate.to(dev, dtype)
-        got = ops.head_linear(xd, wd, K + tail, tail=tail, cos=torch.cos(ang).to(dev), sin=torch.sin(ang).to(dev),
-                              interleaved=True, gate=gd, gate_off=5).float().cpu().view(T, H, N + tail)
-        xr, wr, gr = xd.float().cpu().view(T, H, K + tail), wd.float().cpu(), gd.float().cpu()
-        want = torch.einsum("thk,hnk->thn", xr[..., :K], wr) * torch.sigmoid(gr[:, 5:5 + H])[..., None]
-        a, b = xr[..., K::2], xr[..., K + 1::2]
-        c, s = torch.cos(ang)[:, None], torch.sin(ang)[:, None]
-        turned = torch.stack([a * c - b * s, b * c + a * s], -1).reshape(T, H, tail)                 # (the copied columns are not gated)
-        assert (got[..., :N] - want).abs().max() <= tol * max(1.0, want.abs().max())
-        assert (got[..., N:] - turned).abs().max() <= tol * max(1.0, turned.abs().max())
+    # (sizes the tensor-core form of the product does not take, then sizes it does: two tiles of tokens, two of outputs)
+    for T, H, N, K, tail in ((70, 3, 20, 12, 6), (70, 3, 72, 32, 8), (5, 2, 16, 80, 0)):
+        x = torch.randn(T, H * (K + tail), generator=g)
+        w = torch.randn(H, N, K, generator=g)
+        ang = torch.randn(T, tail // 2, generator=g)
+        gate = torch.randn(T, 5 + H, generator=g)
+        for dtype, tol in ((torch.float32, 1e-5), (torch.bfloat16, 3e-2)):
+            xd, wd, gd = x.to(dev, dtype), w.to(dev, dtype), gate.to(dev, dtype)
+            kw = dict(cos=torch.cos(ang).to(dev), sin=torch.sin(ang).to(dev)) if tail else {}
+            got = ops.head_linear(xd, wd, K + tail, tail=tail, interleaved=True, gate=gd, gate_off=5, **kw).float().cpu().view(T, H, N + tail)
+            xr, wr, gr = xd.float().cpu().view(T, H, K + tail), wd.float().cpu(), gd.float().cpu()
+            want = torch.einsum("thk,hnk->thn", xr[..., :K], wr) * torch.sigmoid(gr[:, 5:5 + H])[..., None]
+            assert (got[..., :N] - want).abs().max() <= tol * max(1.0, want.abs().max()), (T, H, N, K, dtype)
+            if tail:
+                a, b = xr[..., K::2], xr[..., K + 1::2]
+                c, s = torch.cos(ang)[:, None], torch.sin(ang)[:, None]
+                turned = torch.stack([a * c - b * s, b * c + a * s], -1).reshape(T, H, tail)        # (the copied columns are not gated)
+                assert (got[..., N:] - turned).abs().max() <= tol * max(1.0, turned.abs().max())
     logits = torch.randn(50, 7, generator=g)
     bias = torch.randn(7, generator=g)
     ids, weights = ops.moe_route(logits.to(dev), 3, bias=bias.to(dev), softmax_chosen=True)
