@@ -182,7 +182,7 @@ def darusun_model_spec(cfg: DarusunConfig) -> ModelSpec:
         ffn = _feed_forward(cfg, L.get("mlp"), where + ".mlp")
         layers.append(BlockSpec(arrangement="post_norm", norm=norm, mixer=mixer, ffn=ffn,
                                 norm2=norm if ffn is not None else None,
-                                extra=(("branch_scale", cfg.residual_mult),)))
+                                extra=(("branch_scale", cfg.residual_mult), ("hand_on_rounded", True))))
         source = m.get("kv_from") if L["type"] == "attention" else None
         if source is None:
             schedule.append(ScheduleEntry(layer=i, cache=i))

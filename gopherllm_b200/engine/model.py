@@ -188,6 +188,8 @@ class DecoderModel:
         for e in self.spec.schedule[start:stop]:
             view = cache.view(e.cache, e.writes) if e.cache is not None else None
             block = self.blocks[e.layer]
+            if not getattr(block, "takes_rounded_stream", False) or e.enter is not None:
+                ctx.scratch.pop("stream_rounded", None)      # (a rounded copy of the stream a layer left for the next one)
             if e.enter is not None:
                 ops.enter_pass(x, ctx.scratch["embedding_output"] if e.enter.add_embedding else None,
                                self.pass_vectors, e.enter.index)

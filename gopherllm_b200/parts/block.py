@@ -202,7 +202,12 @@ class PostNormBlock(AssembledBlock):
     without a feed-forward (``spec.ffn`` None, no norm2) is the first half alone.  A mixer that offers
     ``branches`` (two outputs with a factor each) is summed in the pass that norms and adds; that pass also
     leaves the stream's rounded copy for the feed-forward.  Option ``branch_scale`` m: x <- x + m * norm(...) for
-    both sublayers (the factor is taken into the norms' weights once, when they are loaded)."""
+    both sublayers (the factor is taken into the norms' weights once, when they are loaded).  Option
+    ``hand_on_rounded``: the pass that closes the layer also leaves the stream's rounded copy in the step's context, and
+    the next layer of this kind takes it from there instead of rounding the stream again (the model drops the copy
+    before a layer that does not take it)."""
+
+    takes_rounded_stream = True
 
     def __init__(self, spec: BlockSpec):
         if (spec.ffn is None) != (spec.norm2 is None):
@@ -212,6 +217,7 @@ class PostNormBlock(AssembledBlock):
             if n is not None and not (getattr(n, "rms", False) and n.fusable is not None and not n.spec.bias):
                 raise ValueError("a block that norms its sublayers' outputs takes RMS norms without bias")
         self.branch_scale = float(spec.option("branch_scale", 1.0))
+        self.hand_on = bool(spec.option("hand_on_rounded", False))
         self.w1 = self.w2 = None                 # the norms' weights times the factor
 
     def load(self, tensors: Dict[str, torch.Tensor]) -> None:
@@ -222,7 +228,10 @@ class PostNormBlock(AssembledBlock):
                 self.w2 = (self.norm2.fusable()[0] * self.branch_scale).contiguous()
 
     def forward(self, x, ctx, cache):
-        h = ops.round_rows(x, ctx.act_dtype)
+        h = ctx.scratch.pop("stream_rounded", None)
+        if h is None or h.shape != x.shape or h.dtype != ctx.act_dtype:
+            h = ops.round_rows(x, ctx.act_dtype)
+        hand_on = ctx.act_dtype if self.hand_on and ctx.act_dtype != torch.float32 else None
         w, _, eps, _ = self.norm.fusable()
         if self.w1 is not None:
             w = self.w1
@@ -230,17 +239,22 @@ class PostNormBlock(AssembledBlock):
         branches = getattr(self.mixer, "branches", None)
         if branches is not None:
             (a, sa), (b, sb) = branches(h, ctx, cache)
-            _, h = ops.post_norm_add(a, w, eps, add=x, out=x, scale=sa, second=(b, sb), rounded=copy)
+            _, h = ops.post_norm_add(a, w, eps, add=x, out=x, scale=sa, second=(b, sb),
+                                     rounded=copy if self.ffn is not None else hand_on)
         else:
             y = self.mixer.forward(h, ctx, cache, (), None)
-            _, h = ops.post_norm_add(y, w, eps, add=x, out=x, rounded=copy)
+            _, h = ops.post_norm_add(y, w, eps, add=x, out=x, rounded=copy if self.ffn is not None else hand_on)
         if self.ffn is None:
+            if hand_on is not None:
+                ctx.scratch["stream_rounded"] = h
             return x
         w2, _, eps2, _ = self.norm2.fusable()
         if self.w2 is not None:
             w2 = self.w2
         y = self.ffn.forward(h if h is not None else x, ctx, (), None)
-        ops.post_norm_add(y, w2, eps2, add=x, out=x)
+        _, h = ops.post_norm_add(y, w2, eps2, add=x, out=x, rounded=hand_on)
+        if hand_on is not None:
+            ctx.scratch["stream_rounded"] = h
         return x
 
 
