@@ -67,16 +67,17 @@ __device__ __forceinline__ float am_shape(float dot, const MixedAttnArgs& a, flo
 #define AM_ROWS 8
 
 // Prompts: one warp owns one query row of one pair; the warps of a block are consecutive tokens of a
-// sequence and share the key and value tiles staged in shared memory.
+// sequence and share the key and value tiles staged in shared memory: a page at a time, or (``stage_rows`` 32, for
+// key rows too long for a whole page of them to fit) half a page at a time.
 template <typename TA, typename TC, int NACC>
 __global__ void __launch_bounds__(AM_ROWS * 32)
-attn_pairs_kernel(MixedAttnArgs a) {
+attn_pairs_kernel(MixedAttnArgs a, int stage_rows) {
     extern __shared__ float smem[];
     gl_grid_wait();
     const int hd = a.hd, vd = a.vd, ks = hd + 1;
-    float* Ks = smem;                       // [GL_PAGE][hd+1]
-    float* Vs = Ks + GL_PAGE * ks;          // [GL_PAGE][vd]
-    float* Qs = Vs + GL_PAGE * vd;          // [AM_ROWS][hd]
+    float* Ks = smem;                       // [stage_rows][hd+1]
+    float* Vs = Ks + stage_rows * ks;       // [stage_rows][vd]
+    float* Qs = Vs + stage_rows * vd;       // [AM_ROWS][hd]
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int b = blockIdx.z;
     const int nVal = a.mix ? a.nKV : 1;
@@ -114,20 +115,21 @@ attn_pairs_kernel(MixedAttnArgs a) {
         const TC* kp = (const TC*)a.k_cache + ((size_t)page * a.nKV + kh) * GL_PAGE * hd;
         const int vs = am_value_stride(a);
         const TC* vp = (const TC*)a.v_cache + ((size_t)page * nvh + vh) * GL_PAGE * vs;
-        const int j0 = page_i * GL_PAGE;
+        for (int row0s = 0; row0s < GL_PAGE; row0s += stage_rows) {
+        const int j0 = page_i * GL_PAGE + row0s;
         __syncthreads();
-        for (int e = threadIdx.x; e < GL_PAGE * hd; e += blockDim.x) {
+        for (int e = threadIdx.x; e < stage_rows * hd; e += blockDim.x) {
             const int r = e / hd, d = e - r * hd;
-            Ks[r * ks + d] = j0 + r < total ? gl_load(kp + e) : 0.f;      // rows past the sequence were never written
+            Ks[r * ks + d] = j0 + r < total ? gl_load(kp + (size_t)row0s * hd + e) : 0.f;      // rows past the sequence were never written
         }
-        for (int e = threadIdx.x; e < GL_PAGE * vd; e += blockDim.x) {
+        for (int e = threadIdx.x; e < stage_rows * vd; e += blockDim.x) {
             const int r = e / vd;
-            Vs[e] = j0 + r < total ? gl_load(vp + (size_t)r * vs + (e - r * vd)) : 0.f;
+            Vs[e] = j0 + r < total ? gl_load(vp + (size_t)(row0s + r) * vs + (e - r * vd)) : 0.f;
         }
         __syncthreads();
         if (!live) continue;
 #pragma unroll 1
-        for (int half = 0; half < GL_PAGE / 32; ++half) {
+        for (int half = 0; half < stage_rows / 32; ++half) {
             const int jj = half * 32 + lane, j = j0 + jj;
             const bool ok = j >= lo && j <= p;
             float s = -INFINITY;
@@ -154,6 +156,7 @@ attn_pairs_kernel(MixedAttnArgs a) {
                     if (d < vd) acc[i] = fmaf(pk, vr[k * vd + d], acc[i]);
                 }
             }
+        }
         }
     }
     if (!live) return;
@@ -514,7 +517,12 @@ static int launch_mixed(const MixedAttnArgs& a, cudaStream_t stream) {
         const size_t smem = ((size_t)a.hd + (size_t)AM_DWARPS * (a.vd + 2)) * sizeof(float);
         rc = gl_launch(attn_pairs_decode_kernel<TA, TC, NACC>, dim3(pairs, a.B), dim3(AM_DWARPS * 32), smem, stream, 1, a);
     } else {
-        const size_t smem = ((size_t)GL_PAGE * (a.hd + 1) + (size_t)GL_PAGE * a.vd + (size_t)AM_ROWS * a.hd) * sizeof(float);
+        size_t smem = ((size_t)GL_PAGE * (a.hd + 1) + (size_t)GL_PAGE * a.vd + (size_t)AM_ROWS * a.hd) * sizeof(float);
+        int stage_rows = GL_PAGE;
+        if (smem > 200 * 1024) {                    // long key rows: half a page of them at a time
+            stage_rows = 32;
+            smem = ((size_t)32 * (a.hd + 1) + (size_t)32 * a.vd + (size_t)AM_ROWS * a.hd) * sizeof(float);
+        }
         auto kern = attn_pairs_kernel<TA, TC, NACC>;
         if (smem > 48 * 1024) {
             if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
@@ -522,7 +530,7 @@ static int launch_mixed(const MixedAttnArgs& a, cudaStream_t stream) {
                 return GL_ERR_SMEM;
             }
         }
-        rc = gl_launch(kern, dim3((a.max_qlen + AM_ROWS - 1) / AM_ROWS, pairs, a.B), dim3(AM_ROWS * 32), smem, stream, 1, a);
+        rc = gl_launch(kern, dim3((a.max_qlen + AM_ROWS - 1) / AM_ROWS, pairs, a.B), dim3(AM_ROWS * 32), smem, stream, 1, a, stage_rows);
     }
     if (rc != 0) return rc;
     const long long n = (long long)a.T * a.nH * a.vd;
@@ -572,7 +580,7 @@ static int dispatch_mixed(const MixedAttnArgs& a, cudaStream_t stream) {
 GL_API int gl_attention_mixed(const MixedAttnArgs* args, int act_dtype, int cache_dtype, cudaStream_t stream) {
     const MixedAttnArgs& a = *args;
     if (a.B <= 0 || a.max_qlen <= 0 || a.T <= 0) return GL_OK;
-    if (a.hd <= 0 || a.hd > 512 || a.vd <= 0 || a.vd > 256 || a.nH <= 0 || a.nKV <= 0 || a.nH % a.nKV) return GL_ERR_SHAPE;
+    if (a.hd <= 0 || a.hd > 1024 || a.vd <= 0 || a.vd > 256 || a.nH <= 0 || a.nKV <= 0 || a.nH % a.nKV) return GL_ERR_SHAPE;
     if (a.nVH < 0 || (a.nVH > 0 && (a.nVH % a.nKV || a.nH % a.nVH || (a.mix && a.nVH != a.nKV)))) return GL_ERR_SHAPE;
     if (a.vs < 0 || (a.vs > 0 && a.vs < a.vd)) return GL_ERR_SHAPE;
     if (a.B > 65535 || a.nH * a.nKV > 65535) return GL_ERR_SHAPE;

@@ -50,6 +50,8 @@ struct PairsArgs {
                               // table, query head h then takes the values of head h / (nH / nVH)
     int vs;                   // numbers between two positions' values of a head (0: the value size); a cache whose values
                               // are the first columns of its key rows is read with v_cache = k_cache and vs = the key size
+    int v_in_k;               // such a cache with one row of values a key head: no value tile is fetched, the second
+                              // product reads the key tile
 };
 
 __device__ __forceinline__ unsigned ap_smem(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
@@ -100,9 +102,11 @@ __device__ __forceinline__ void ap_load_rows(unsigned dst, const __nv_bfloat16* 
 __global__ void __launch_bounds__(AP_THREADS)
 attn_pairs_tc_kernel(PairsArgs a) {
     extern __shared__ __align__(16) unsigned char smem[];
-    const unsigned sQ = ap_smem(smem);
-    const unsigned sK[2] = {sQ + AP_TILE, sQ + 2 * AP_TILE};
-    const unsigned sV[2] = {sQ + 3 * AP_TILE, sQ + 3 * AP_TILE + AP_VTILE};
+    // (the query tile passes through the second key stage before the first page is asked for: a block's shared
+    // memory is two key stages and two value stages, so that two or three blocks fit an SM at long key rows)
+    const unsigned sK[2] = {ap_smem(smem), ap_smem(smem) + AP_TILE};
+    const unsigned sQ = sK[1];
+    const unsigned sV[2] = {sK[0] + 2 * AP_TILE, sK[0] + 2 * AP_TILE + AP_VTILE};
     gl_grid_wait();                                            // (a long kernel: the next one is not launched early)
     const int b = blockIdx.z;
     const int h = blockIdx.y / a.nVal;                         // query head
@@ -129,16 +133,25 @@ attn_pairs_tc_kernel(PairsArgs a) {
     const size_t vhead_off = (size_t)vh * GL_PAGE * vs, vpage_stride = (size_t)nvh * GL_PAGE * vs;
     const int total = ctx + qlen;
 
-    // the query tile, then the first page
+    // the query tile and the first page; the tile's fragments go to registers before its stage is used for keys
     ap_load_rows<AP_HD>(sQ, (const __nv_bfloat16*)a.q + ((size_t)(qstart + q0) * a.nH + h) * AP_HD, (size_t)a.nH * AP_HD, rows);
     {
         const int nv = min(GL_PAGE, total - page_begin * GL_PAGE);
         ap_load_rows<AP_HD>(sK[0], K + (size_t)pg[page_begin] * page_stride + head_off, AP_HD, nv);
-        ap_load_rows<AP_VD>(sV[0], V + (size_t)pg[page_begin] * vpage_stride + vhead_off, vs, nv);
+        if (!a.v_in_k) ap_load_rows<AP_VD>(sV[0], V + (size_t)pg[page_begin] * vpage_stride + vhead_off, vs, nv);
     }
     ap_commit();
+    ap_wait<0>();
+    __syncthreads();
 
     unsigned qf[AP_KS][4];
+#pragma unroll
+    for (int kk = 0; kk < AP_KS; ++kk) {
+        const int r = (threadIdx.x >> 5) * 16 + (threadIdx.x & 7) + ((threadIdx.x >> 3) & 1) * 8;
+        const int c = kk * 2 + ((threadIdx.x & 31) >> 4);
+        ap_ldm4(sQ + r * AP_ROW + c * 16, qf[kk][0], qf[kk][1], qf[kk][2], qf[kk][3]);
+    }
+    __syncthreads();
     float o[AP_NT][4];
 #pragma unroll
     for (int i = 0; i < AP_NT; ++i)
@@ -159,19 +172,11 @@ attn_pairs_tc_kernel(PairsArgs a) {
         if (p + 1 < page_end) {
             const int nv = min(GL_PAGE, total - (p + 1) * GL_PAGE);
             ap_load_rows<AP_HD>(sK[st ^ 1], K + (size_t)pg[p + 1] * page_stride + head_off, AP_HD, nv);
-            ap_load_rows<AP_VD>(sV[st ^ 1], V + (size_t)pg[p + 1] * vpage_stride + vhead_off, vs, nv);
+            if (!a.v_in_k) ap_load_rows<AP_VD>(sV[st ^ 1], V + (size_t)pg[p + 1] * vpage_stride + vhead_off, vs, nv);
         }
         ap_commit();
         ap_wait<1>();
         __syncthreads();
-        if (p == page_begin) {
-#pragma unroll
-            for (int kk = 0; kk < AP_KS; ++kk) {
-                const int r = warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
-                const int c = kk * 2 + (lane >> 4);
-                ap_ldm4(sQ + r * AP_ROW + c * 16, qf[kk][0], qf[kk][1], qf[kk][2], qf[kk][3]);
-            }
-        }
         const int j0 = p * GL_PAGE;
         // a warp whose rows all lie before this page has nothing to do here (causal)
         const bool warp_active = j0 <= p_first + warp * 16 + 15;
@@ -265,7 +270,7 @@ attn_pairs_tc_kernel(PairsArgs a) {
                     unsigned b0, b1, b2, b3;
                     const int r = kk * 16 + ((lane >> 3) & 1) * 8 + (lane & 7);
                     const int c = dn + (lane >> 4);
-                    ap_ldm4t(sV[st] + r * AP_VROW + c * 16, b0, b1, b2, b3);
+                    ap_ldm4t((a.v_in_k ? sK[st] + r * AP_ROW : sV[st] + r * AP_VROW) + c * 16, b0, b1, b2, b3);
                     ap_mma(o[dn], pa, b0, b1);
                     ap_mma(o[dn + 1], pa, b2, b3);
                 }
@@ -552,15 +557,16 @@ GL_API int gl_attention_pairs_tc(const PairsArgs* args, cudaStream_t stream) {
     if (a.nH <= 0 || a.nKV <= 0 || a.nH % a.nKV || (a.nVal != 1 && a.nVal != a.nKV)) return GL_ERR_SHAPE;
     if (a.nVH < 0 || (a.nVH > 0 && (a.nH % a.nVH || (a.nVal != 1 && a.nVH != a.nKV)))) return GL_ERR_SHAPE;
     if (a.vs < 0 || (a.vs > 0 && (a.vs < AP_VD || a.vs % 8))) return GL_ERR_SHAPE;
+    if (a.v_in_k && (AP_VD > AP_HD || a.nVal != 1 || (a.nVH > 0 && a.nVH != a.nKV))) return GL_ERR_SHAPE;
     if (a.B > 65535 || a.nH * a.nVal > 65535) return GL_ERR_SHAPE;
-    const size_t smem = 3 * (size_t)AP_TILE + 2 * (size_t)AP_VTILE;
-    static bool configured = false;
-    if (!configured) {
+    const size_t smem = 2 * (size_t)AP_TILE + (a.v_in_k ? 0 : 2 * (size_t)AP_VTILE);
+    static size_t configured = 0;
+    if (smem > configured) {
         if (cudaFuncSetAttribute(attn_pairs_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
             cudaGetLastError();
             return GL_ERR_SMEM;
         }
-        configured = true;
+        configured = smem;
     }
     dim3 grid((a.max_qlen + AP_BM - 1) / AP_BM, a.nH * a.nVal, a.B);
     return gl_launch(attn_pairs_tc_kernel, grid, dim3(AP_THREADS), smem, stream, 1, a) == 0 ? GL_OK : GL_ERR_LAUNCH;

@@ -273,6 +273,10 @@ qkv_rownorm_cache_kernel(QkvRowNormArgs a) {
     extern __shared__ float smem[];
     __shared__ float red[16];
     gl_grid_launch_dependents();
+    // the table that mixes the heads' scores is a weight: it comes into shared memory while the kernel before drains
+    float* talk = smem + (size_t)(a.nH + a.nKV) * a.hd;
+    if (a.talk)
+        for (int i = threadIdx.x; i < a.nH * a.nH; i += blockDim.x) talk[i] = a.talk[i];
     gl_grid_wait();
     const int t = blockIdx.x;
     const int nq = a.nH * a.hd, nk = a.q_only ? 0 : a.nKV * a.hd, nv = a.q_only ? 0 : a.nKV * a.vd;
@@ -343,14 +347,20 @@ qkv_rownorm_cache_kernel(QkvRowNormArgs a) {
         // while the heads of the result are walked; the table's entries are the same for all threads of a step
         const int wide = a.nKV * a.hd, per = a.nH / a.nKV;
         TA* qo = (TA*)a.q_out + (size_t)t * a.nH * wide;
-        for (int r = threadIdx.x; r < wide; r += blockDim.x) {
+        // where the block has more threads than the rows have columns, the heads of the result are shared out too
+        int parts = (int)blockDim.x / wide;
+        if (parts < 1 || a.nH % parts) parts = 1;
+        const int heads_each = a.nH / parts;
+        for (int item = threadIdx.x; item < wide * parts; item += blockDim.x) {
+            const int part = item / wide, r = item - part * wide;
             const int c = r / a.hd, d = r - c * a.hd;
+            const int h_first = part * heads_each, h_end = h_first + heads_each;
             if (per <= 8) {
                 float qg[8];
 #pragma unroll
                 for (int g = 0; g < 8; ++g) qg[g] = g < per ? v[(size_t)(c * per + g) * a.hd + d] * q_mul : 0.f;
-                for (int h = 0; h < a.nH; ++h) {
-                    const float* row = a.talk + (size_t)h * a.nH + c * per;
+                for (int h = h_first; h < h_end; ++h) {
+                    const float* row = talk + (size_t)h * a.nH + c * per;
                     float y = 0.f;
 #pragma unroll
                     for (int g = 0; g < 8; ++g)
@@ -358,9 +368,9 @@ qkv_rownorm_cache_kernel(QkvRowNormArgs a) {
                     gl_store(qo + (size_t)h * wide + r, y);
                 }
             } else {
-                for (int h = 0; h < a.nH; ++h) {
+                for (int h = h_first; h < h_end; ++h) {
                     float y = 0.f;
-                    for (int g = c * per; g < (c + 1) * per; ++g) y = fmaf(a.talk[h * a.nH + g], v[(size_t)g * a.hd + d], y);
+                    for (int g = c * per; g < (c + 1) * per; ++g) y = fmaf(talk[h * a.nH + g], v[(size_t)g * a.hd + d], y);
                     gl_store(qo + (size_t)h * wide + r, y * q_mul);
                 }
             }
@@ -388,10 +398,11 @@ GL_API int gl_qkv_rownorm_cache(const QkvRowNormArgs* args, int act_dtype, int c
     const QkvRowNormArgs& a = *args;
     if (a.T <= 0) return GL_OK;
     if (a.hd <= 0 || a.vd <= 0 || a.nH <= 0 || a.nKV <= 0 || 2 * a.half > a.hd) return GL_ERR_SHAPE;
-    const size_t smem = (size_t)(a.nH + a.nKV) * a.hd * sizeof(float);
+    const size_t smem = ((size_t)(a.nH + a.nKV) * a.hd + (a.talk ? (size_t)a.nH * a.nH : 0)) * sizeof(float);
     if (smem > 200 * 1024) return GL_ERR_SMEM;
-    // few tokens: more threads a token, so that a row's loads are in flight together
-    const dim3 g((unsigned)a.T), b(a.T <= 256 && (a.nH + a.nKV) * a.hd >= 2048 ? 512 : 128);
+    // few tokens: more threads a token, so that a row's loads are in flight together; a table on the queries: a thread
+    // a column of the wide rows
+    const dim3 g((unsigned)a.T), b(a.T <= 256 && (a.nH + a.nKV) * a.hd >= 2048 ? 512 : (a.talk && a.nKV * a.hd >= 256 ? 256 : 128));
     if (act_dtype != cache_dtype || (act_dtype != GL_F32 && act_dtype != GL_BF16)) return GL_ERR_DTYPE;
     if (smem > 48 * 1024) {                           // (many wide heads: a block may ask for more than the default)
         const cudaError_t e = act_dtype == GL_F32

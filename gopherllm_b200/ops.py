@@ -1337,7 +1337,7 @@ class _PairsArgs(Structure):
                 ("seq_qstart", c_void_p), ("seq_qlen", c_void_p), ("seq_ctx", c_void_p), ("pages", c_void_p),
                 ("B", c_int), ("nH", c_int), ("nKV", c_int), ("nVal", c_int), ("max_pages", c_int), ("window", c_int),
                 ("max_qlen", c_int), ("score_scale", c_float), ("softcap", c_float), ("slopes", c_void_p),
-                ("out", c_void_p), ("sinks", c_void_p), ("nVH", c_int), ("vs", c_int)]
+                ("out", c_void_p), ("sinks", c_void_p), ("nVH", c_int), ("vs", c_int), ("v_in_k", c_int)]
 
 
 USE_PAIRS_TC = True
@@ -1406,13 +1406,13 @@ def attention_mixed(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tenso
     out = empty((T, num_heads * value_dim), q.dtype, q.device)
     pairs_tc = (USE_PAIRS_TC and ctx.max_qlen > 1 and q.dtype == torch.bfloat16 and k_cache.dtype == torch.bfloat16
                 and head_dim % 16 == 0 and value_dim % 16 == 0 and head_dim <= 256 and value_dim <= 256
-                and 3 * 64 * (2 * head_dim + 16) + 2 * 64 * (2 * value_dim + 16) <= 227 * 1024 and not DEBUG_BOUNDS)
+                and 2 * 64 * (2 * head_dim + 16) + 2 * 64 * (2 * value_dim + 16) <= 227 * 1024 and not DEBUG_BOUNDS)
     if pairs_tc and mix is None:
         # prompts without a mixing table: the tensor-core kernel rounds and writes the result itself
         p = _PairsArgs(q.data_ptr(), None, k_cache.data_ptr(), v_cache.data_ptr(),
                        ctx.seq_qstart.data_ptr(), ctx.seq_qlen.data_ptr(), ctx.seq_ctx.data_ptr(), pages.data_ptr(),
                        ctx.n_seqs, num_heads, num_kv_heads, 1, pages.shape[-1], window, ctx.max_qlen,
-                       score_scale, softcap, _addr(slopes), out.data_ptr(), _addr(sinks), nvh, vs)
+                       score_scale, softcap, _addr(slopes), out.data_ptr(), _addr(sinks), nvh, vs, 1 if values_in_keys else 0)
         fn = _lib("attention_mixed_tc.cu", catalog.pair_dim_defines(head_dim, value_dim)).gl_attention_pairs_tc
         _check(_launch(fn, byref(p), _stream()), "attention_pairs_tc")
         return out
@@ -1467,7 +1467,7 @@ def attention_mixed(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tenso
         p = _PairsArgs(q.data_ptr(), pairs.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(),
                        ctx.seq_qstart.data_ptr(), ctx.seq_qlen.data_ptr(), ctx.seq_ctx.data_ptr(), pages.data_ptr(),
                        ctx.n_seqs, num_heads, num_kv_heads, n_val, pages.shape[-1], window, ctx.max_qlen,
-                       score_scale, softcap, _addr(slopes), None, _addr(sinks), nvh, vs)
+                       score_scale, softcap, _addr(slopes), None, _addr(sinks), nvh, vs, 0)
         fn = _lib("attention_mixed_tc.cu", catalog.pair_dim_defines(head_dim, value_dim)).gl_attention_pairs_tc
         _check(_launch(fn, byref(p), _stream()), "attention_pairs_tc")
         _check(_launch(lib.gl_head_mix, byref(a), c_int(dtype_code(q.dtype)), _stream()), "head_mix")

@@ -173,9 +173,9 @@ class MixedHeadAttention(Mixer):
         self.vdim = spec.value_dim or spec.head_dim
         self.talk_scores = bool(spec.option("talk_scores", False))
         if self.talk_scores:
-            if spec.head_dim * spec.num_kv_heads > 512 or self.vdim > 256:
+            if spec.head_dim * spec.num_kv_heads > 1024 or self.vdim > 256:
                 raise ValueError(f"{spec.num_kv_heads} key heads of {spec.head_dim} side by side exceed what the attention "
-                                 f"kernels take (512), or values of {self.vdim} do (256)")
+                                 f"kernels take (1024), or values of {self.vdim} do (256)")
             if spec.option("talk", False):
                 raise ValueError("a table mixes the heads' scores or their softmax weights, not both")
         elif spec.head_dim > 256 or self.vdim > 256:
@@ -334,8 +334,8 @@ class LatentAttention(Mixer):
             raise ValueError("latent attention: ranks, heads and head sizes are positive, the rotated part is even")
         if spec.position.kind != "none" and spec.position.rotary_dim != self.rot:
             raise ValueError("latent attention: the rotation covers the rotated part exactly")
-        if self.kv_rank + self.rot > 512 or self.kv_rank > 256:
-            raise ValueError(f"a latent of {self.kv_rank} + {self.rot} exceeds what the attention kernels take (256 + 256)")
+        if self.kv_rank + self.rot > 1024 or self.kv_rank > 256:
+            raise ValueError(f"a latent of {self.kv_rank} + {self.rot} exceeds what the attention kernels take (256 + 768)")
         self.sink = bool(spec.option("sink", False))
         self.gate = bool(spec.option("gate", False))
         self.eps = float(spec.option("norm_eps", 1e-6))

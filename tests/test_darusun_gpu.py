@@ -137,6 +137,13 @@ ROWS = dict(
          "mlp": None},
     ])
 
+# key rows too long for a page of them in shared memory: four key heads of 160 side by side
+LONG_ROWS = dict(
+    architecture="Darusun", vocab=120, width=48, norm={"eps": 1e-6}, residual_mult=1.0,
+    layers=[{"type": "attention",
+             "mixer": {"heads": 4, "kv_heads": 4, "dim": 160, "vdim": 8, "scale": 0.1, "rot": {"dims": 6, "base": 100.0}},
+             "mlp": None}])
+
 ALONE = [("talking_heads_with_shared_expert", dm.only(dm.ALPHA, 0)), ("latent_dense", dm.only(dm.ALPHA, 1)),
          ("talking_heads_bare", dm.only(dm.ALPHA, 2, mlp=False)), ("latent_top1", dm.only(dm.ALPHA, 3)),
          ("latent_small_rotation_long_window", dm.only(dm.BETA, 0)), ("talking_full_rotation_top3", dm.only(dm.BETA, 1)),
@@ -145,7 +152,7 @@ ALONE = [("talking_heads_with_shared_expert", dm.only(dm.ALPHA, 0)), ("latent_de
          ("latent_sixteen_heads", dm.only(MANY, 0)), ("talking_sixteen_on_two", dm.only(MANY, 1)),
          ("talking_sixteen_on_eight", dm.only(MANY, 2)), ("talking_twelve_on_three", dm.only(MANY, 3)), ("many_heads", MANY),
          ("rows_latent_sixteen", dm.only(ROWS, 0)), ("rows_talking_runs_of_eight", dm.only(ROWS, 1)),
-         ("rows_talking_runs_of_four", dm.only(ROWS, 2)), ("rows_latent_no_rotation_no_window", dm.only(ROWS, 3)), ("rows", ROWS)]
+         ("rows_talking_runs_of_four", dm.only(ROWS, 2)), ("rows_latent_no_rotation_no_window", dm.only(ROWS, 3)), ("rows", ROWS), ("talking_long_key_rows", LONG_ROWS)]
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
