@@ -448,11 +448,41 @@ gated_act_rows_kernel(const TA* gu, TA* __restrict__ out, long long n, int F, in
     }
 }
 
+// bfloat16 rows whose halves and whose length are whole 16-byte units: eight columns a thread
+__global__ void __launch_bounds__(256)
+gated_act_rows_bf16x8_kernel(const __nv_bfloat16* gu, __nv_bfloat16* __restrict__ out, long long n8, int F8, int ld, int row_gate, int act) {
+    gl_grid_launch_dependents();
+    gl_grid_wait();
+    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n8; i += (long long)gridDim.x * blockDim.x) {
+        const long long t = i / F8;
+        const int j = (int)(i - t * F8);
+        const __nv_bfloat16* rowp = gu + (size_t)t * ld;
+        const uint4* row = (const uint4*)rowp;
+        const uint4 g = row[j], u = row[F8 + j];
+        const float share = row_gate >= 0 ? 1.0f / (1.0f + expf(-__bfloat162float(rowp[row_gate]))) : 1.0f;
+        const __nv_bfloat162* g2 = (const __nv_bfloat162*)&g;
+        const __nv_bfloat162* u2 = (const __nv_bfloat162*)&u;
+        uint4 o;
+        __nv_bfloat162* o2 = (__nv_bfloat162*)&o;
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const float2 gf = __bfloat1622float2(g2[e]), uf = __bfloat1622float2(u2[e]);
+            o2[e] = __floats2bfloat162_rn(gl_activate<true>(gf.x, act) * uf.x * share, gl_activate<true>(gf.y, act) * uf.y * share);
+        }
+        ((uint4*)out)[i] = o;
+    }
+}
+
 GL_API int gl_gated_act_rows(const void* gu, void* out, int T, int F, int ld, int row_gate, int act, int act_dtype,
                              cudaStream_t stream) {
     if (T <= 0) return GL_OK;
     if (F <= 0 || ld < 2 * F || row_gate >= ld) return GL_ERR_SHAPE;
     const long long n = (long long)T * F;
+    if (act_dtype == GL_BF16 && F % 8 == 0 && ld % 8 == 0 && !(((uintptr_t)gu | (uintptr_t)out) & 15)) {
+        const long long n8 = n / 8, want8 = (n8 + 255) / 256;
+        return gl_launch(gated_act_rows_bf16x8_kernel, dim3((unsigned)(want8 > 8192 ? 8192 : want8)), dim3(256), 0, stream, 1,
+                         (const __nv_bfloat16*)gu, (__nv_bfloat16*)out, n8, F / 8, ld, row_gate, act);
+    }
     const long long want = (n + 255) / 256;
     const dim3 grid((unsigned)(want > 8192 ? 8192 : want));
     if (act_dtype == GL_F32)
