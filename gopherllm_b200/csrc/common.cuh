@@ -17,7 +17,9 @@ enum GlDtype { GL_F32 = 0, GL_BF16 = 1 };
 // activation applied in an epilogue
 enum GlAct { GL_ACT_NONE = 0, GL_ACT_GELU_TANH = 1, GL_ACT_GELU_ERF = 2, GL_ACT_RELU = 3,
              GL_ACT_RELU_SQ = 4,      // max(x, 0)^2
-             GL_ACT_SILU = 5 };       // x * sigmoid(x)
+             GL_ACT_SILU = 5,         // x * sigmoid(x)
+             GL_ACT_XIELU = 6 };      // two numbers (up, down) come with it: up x^2 + x/2 above zero,
+                                      // down (e^x - 1 - x) + x/2 at and below zero
 
 // error codes
 enum GlError {
@@ -163,6 +165,20 @@ __device__ __forceinline__ float gl_activate_bf16_grade(float x, int act) {
     return x;
 }
 
+// the activation with two numbers of its own (the same slope on both sides of zero)
+template <bool EXACT>
+__device__ __forceinline__ float gl_xielu(float x, float up, float down) {
+    if (EXACT) {
+        if (x > 0.f) return fmaf(up * x, x, 0.5f * x);
+        return fmaf(down, expm1f(x) - x, 0.5f * x);
+    }
+    // for results that are rounded to 16 bits right away: down e^x - down + (1/2 - down) x, four operations and no
+    // branch (what the difference of the first two terms loses near zero is 2^-22 of ``down``, far below the rounding)
+    const float pos = x * fmaf(up, x, 0.5f);
+    const float neg = fmaf(down, __expf(x), fmaf(0.5f - down, x, -down));
+    return x > 0.f ? pos : neg;
+}
+
 template <bool EXACT>
 __device__ __forceinline__ float gl_activate(float x, int act) {
     switch (act) {
@@ -184,4 +200,13 @@ __device__ __forceinline__ float gl_activate(float x, int act) {
         default:
             return x;
     }
+}
+
+// the same for callers that carry an activation's own numbers along
+template <bool EXACT>
+__device__ __forceinline__ float gl_activate(float x, int act, float p0, float p1) {
+    return act == GL_ACT_XIELU ? gl_xielu<EXACT>(x, p0, p1) : gl_activate<EXACT>(x, act);
+}
+__device__ __forceinline__ float gl_activate_bf16_grade(float x, int act, float p0, float p1) {
+    return act == GL_ACT_XIELU ? gl_xielu<false>(x, p0, p1) : gl_activate_bf16_grade(x, act);
 }

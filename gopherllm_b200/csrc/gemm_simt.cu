@@ -20,6 +20,18 @@ struct GemmArgs {
     const float* add1;    // [M, N] or null, 32-bit
     void* out;            // [M, N]
     int M, N, K, act;
+    // (the rest of the record as the other products read it; only the activation's numbers are used here)
+    const void* a2_unused;
+    const void* w2_unused;
+    const float* bias2_unused;
+    int K2_unused;
+    const void* wB_unused;
+    const float* biasB_unused;
+    void* outB_unused;
+    int NB_unused, actB_unused;
+    const int* group_of_tile_unused;
+    int groups_unused;
+    float act_p0, act_p1;       // the numbers of an activation that has some (GL_ACT_XIELU)
 };
 
 template <typename TA, typename TW, typename TO>
@@ -76,7 +88,7 @@ gemm_simt_kernel(GemmArgs g) {
             if (n >= g.N) continue;
             float v = acc[i][j];
             if (g.bias) v += g.bias[n];
-            v = gl_activate<true>(v, g.act);
+            v = gl_activate<true>(v, g.act, g.act_p0, g.act_p1);
             const size_t o = (size_t)m * g.N + n;
             if (g.add0) v += g.add0[o];
             if (g.add1) v += g.add1[o];

@@ -36,6 +36,14 @@ struct GemmArgs {
     const void* w2;       // [N, K2] bf16
     const float* bias2;   // [N] or null
     int K2;
+    // (the rest of the record as the many-row product reads it; only the activation's numbers are used here)
+    const void* wB_unused;
+    const float* biasB_unused;
+    void* outB_unused;
+    int NB_unused, actB_unused;
+    const int* group_of_tile_unused;
+    int groups_unused;
+    float act_p0, act_p1;       // the numbers of an activation that has some (GL_ACT_XIELU)
 };
 
 __device__ __forceinline__ void ldmatrix_x4(unsigned addr, unsigned& r0, unsigned& r1, unsigned& r2, unsigned& r3) {
@@ -187,7 +195,7 @@ gemm_skinny_kernel(GemmArgs g, int k_per_block, const __grid_constant__ CUtensor
             const float* peer = cluster.map_shared_rank(tile, s);
             v += peer[m * LD + nl];
         }
-        v = gl_activate<false>(v + my_bias, g.act);
+        v = gl_activate<false>(v + my_bias, g.act, g.act_p0, g.act_p1);
         const size_t o = (size_t)m * g.N + my_n;
         if constexpr (MT <= 2) {
             // (indexed with a compile-time number below: the array stays in registers)

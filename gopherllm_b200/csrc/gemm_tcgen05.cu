@@ -55,6 +55,7 @@ struct GemmArgs {
     // experts one product.  Whole tiles of 128 rows only, tile stores only.
     const int* group_of_tile;   // [ceil(M / 128)] or null
     int groups;
+    float act_p0, act_p1;       // the numbers of an activation that has some (GL_ACT_XIELU)
 };
 
 // The work of one block: whole output tiles taken round-robin, or (split) an equal share of all
@@ -292,16 +293,16 @@ gemm_tcgen05_kernel(GemmArgs g, const __grid_constant__ CUtensorMap map_a, const
                     for (int q = 0; q < 8; ++q) {                        // 16-byte chunks, swizzled as TMA expects
                         uint4 pk;
                         if (CW == 32) {
-                            pk.x = __float_as_uint(gl_activate<false>(__uint_as_float(r[4 * q + 0]) + bias_s[c + 4 * q + 0], ACT));
-                            pk.y = __float_as_uint(gl_activate<false>(__uint_as_float(r[4 * q + 1]) + bias_s[c + 4 * q + 1], ACT));
-                            pk.z = __float_as_uint(gl_activate<false>(__uint_as_float(r[4 * q + 2]) + bias_s[c + 4 * q + 2], ACT));
-                            pk.w = __float_as_uint(gl_activate<false>(__uint_as_float(r[4 * q + 3]) + bias_s[c + 4 * q + 3], ACT));
+                            pk.x = __float_as_uint(gl_activate<false>(__uint_as_float(r[4 * q + 0]) + bias_s[c + 4 * q + 0], ACT, g.act_p0, g.act_p1));
+                            pk.y = __float_as_uint(gl_activate<false>(__uint_as_float(r[4 * q + 1]) + bias_s[c + 4 * q + 1], ACT, g.act_p0, g.act_p1));
+                            pk.z = __float_as_uint(gl_activate<false>(__uint_as_float(r[4 * q + 2]) + bias_s[c + 4 * q + 2], ACT, g.act_p0, g.act_p1));
+                            pk.w = __float_as_uint(gl_activate<false>(__uint_as_float(r[4 * q + 3]) + bias_s[c + 4 * q + 3], ACT, g.act_p0, g.act_p1));
                         } else {
                             float v[8];
 #pragma unroll
                             for (int e = 0; e < 8; ++e) {
                                 const unsigned raw = q < 4 ? r[8 * q + e] : r2[8 * (q - 4) + e];
-                                v[e] = gl_activate_bf16_grade(__uint_as_float(raw) + bias_s[c + 8 * q + e], ACT);
+                                v[e] = gl_activate_bf16_grade(__uint_as_float(raw) + bias_s[c + 8 * q + e], ACT, g.act_p0, g.act_p1);
                             }
                             __nv_bfloat162 p0 = __floats2bfloat162_rn(v[0], v[1]), p1 = __floats2bfloat162_rn(v[2], v[3]);
                             __nv_bfloat162 p2 = __floats2bfloat162_rn(v[4], v[5]), p3 = __floats2bfloat162_rn(v[6], v[7]);
@@ -332,7 +333,7 @@ gemm_tcgen05_kernel(GemmArgs g, const __grid_constant__ CUtensorMap map_a, const
                         const int rows_here = min(32, g.M - mrow0);
 #pragma unroll 4
                         for (int rr = 0; rr < rows_here; ++rr) {
-                            float v = gl_activate<false>(patch[rr * 33 + lane] + bv, ACT);
+                            float v = gl_activate<false>(patch[rr * 33 + lane] + bv, ACT, g.act_p0, g.act_p1);
                             const size_t o = (size_t)(mrow0 + rr) * g.N + n;
                             if (g.add0) v += g.add0[o];
                             if (g.add1) v += g.add1[o];
@@ -349,6 +350,7 @@ gemm_tcgen05_kernel(GemmArgs g, const __grid_constant__ CUtensorMap map_a, const
                 case GL_ACT_RELU: store_tile(std::integral_constant<int, GL_ACT_RELU>{}); break;
                 case GL_ACT_RELU_SQ: store_tile(std::integral_constant<int, GL_ACT_RELU_SQ>{}); break;
                 case GL_ACT_SILU: store_tile(std::integral_constant<int, GL_ACT_SILU>{}); break;
+                case GL_ACT_XIELU: store_tile(std::integral_constant<int, GL_ACT_XIELU>{}); break;
                 default: store_tile(std::integral_constant<int, GL_ACT_NONE>{}); break;
             }
             tc_fence_before();

@@ -18,6 +18,7 @@ from .csrc import build, catalog
 
 PAGE = 64                      # tokens per cache page (GL_PAGE)
 F32, BF16 = 0, 1
+# (an activation with numbers of its own travels as a tuple: ("xielu", up, down))
 ACTIVATIONS = {"none": 0, None: 0, "gelu_new": 1, "gelu_pytorch_tanh": 1, "gelu": 2, "relu": 3,
                "relu2": 4,      # the square of relu
                "silu": 5}
@@ -800,7 +801,20 @@ class _GemmArgs(Structure):
                 # a second set of columns from the same rows (tcgen05 kernel only)
                 ("wB", c_void_p), ("biasB", c_void_p), ("outB", c_void_p), ("NB", c_int), ("actB", c_int),
                 # grouped weights (tcgen05 kernel only): the matrix each tile of 128 rows multiplies
-                ("group_of_tile", c_void_p), ("groups", c_int)]
+                ("group_of_tile", c_void_p), ("groups", c_int),
+                # the numbers of an activation that has some (every product kernel reads these two)
+                ("act_p0", c_float), ("act_p1", c_float)]
+
+
+def _act_code(act):
+    """(code, p0, p1) of an activation given by name, or as ("xielu", up, down)."""
+    if isinstance(act, tuple):
+        if len(act) != 3 or act[0] != "xielu":
+            raise KernelError(f"activation {act!r} unknown")
+        return 6, float(act[1]), float(act[2])
+    if act not in ACTIVATIONS:
+        raise KernelError(f"activation {act!r} unknown")
+    return ACTIVATIONS[act], 0.0, 0.0
 
 
 def _gemm_args(a, w, bias, act, add0, add1, out) -> _GemmArgs:
@@ -816,10 +830,9 @@ def _gemm_args(a, w, bias, act, add0, add1, out) -> _GemmArgs:
         if t is not None:
             _need(t, n, torch.float32, (M, N))
     _need(out, "out", shape=(M, N))
-    if act not in ACTIVATIONS:
-        raise KernelError(f"activation {act!r} unknown")
+    code, p0, p1 = _act_code(act)
     return _GemmArgs(a.data_ptr(), w.data_ptr(), _addr(bias), _addr(add0), _addr(add1), out.data_ptr(),
-                     M, N, K, ACTIVATIONS[act], None, None, None, 0, None, None, None, 0, 0, None, 0)
+                     M, N, K, code, None, None, None, 0, None, None, None, 0, 0, None, 0, p0, p1)
 
 
 def gemm_simt(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None, act=None,
@@ -943,7 +956,7 @@ def gemm_tcgen05(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] 
     if fork is not None:
         w_b, bias_b, act_b = fork
         _need(w_b, "wB", torch.bfloat16)
-        if w_b.shape[1] != a.shape[1] or act_b not in ACTIVATIONS:
+        if w_b.shape[1] != a.shape[1] or isinstance(act_b, tuple) or act_b not in ACTIVATIONS:
             raise KernelError(f"second set of columns {tuple(w_b.shape)} does not fit a {tuple(a.shape)}")
         if bias_b is not None:
             _need(bias_b, "biasB", torch.float32, (w_b.shape[0],))
@@ -972,7 +985,7 @@ def gemm_tcgen05_grouped(a: torch.Tensor, w: torch.Tensor, group_of_tile: torch.
         raise KernelError(f"gemm_tcgen05_grouped: a {tuple(a.shape)}, w {tuple(w.shape)} and {group_of_tile.numel()} tiles do not fit")
     out = empty((M, N), out_dtype, a.device)
     g = _GemmArgs(a.data_ptr(), w.data_ptr(), None, None, None, out.data_ptr(), M, N, K, 0,
-                  None, None, None, 0, None, None, None, 0, 0, group_of_tile.data_ptr(), E)
+                  None, None, None, 0, None, None, None, 0, 0, group_of_tile.data_ptr(), E, 0.0, 0.0)
     fn = _lib("gemm_tcgen05.cu").gl_gemm_tcgen05
     _check(_launch(fn, byref(g), c_int(dtype_code(out_dtype)), c_int(tile_n), _stream()), "gemm_tcgen05_grouped")
     return out

@@ -16,9 +16,8 @@ class DenseFeedForward(FeedForward):
     epilogue, the additions to the residual in the second's.
 
     Activation ``xielu`` has two learned numbers p, q (tensor "act" [2]): above zero softplus(p) z^2 + z / 2, at and
-    below zero (1/2 + softplus(q)) (e^z - 1 - z) + z / 2.  The two factors are taken once, when the weights are loaded;
-    the activation is a pass of its own behind the first product (the products' epilogues know activations without
-    numbers of their own)."""
+    below zero (1/2 + softplus(q)) (e^z - 1 - z) + z / 2.  The two factors are taken once, when the weights are loaded,
+    and travel with the activation into the first product's epilogue, like the activations without numbers."""
     capturable = True
     launches_only = True
 
@@ -31,6 +30,7 @@ class DenseFeedForward(FeedForward):
         self.act_up = self.act_down = 0.0
         if self.learned:
             self.fusable = None                      # no block runs this feed-forward inside a fused layer
+            self.first_product = None                # ... or its first product beside another branch's
 
     def parameters(self) -> Dict[str, ParamSpec]:
         s = self.spec
@@ -51,7 +51,7 @@ class DenseFeedForward(FeedForward):
             self.act_up, self.act_down = float(soft[0]), 0.5 + float(soft[1])
 
     def _first_activation(self):
-        return None if self.learned else self.spec.activation
+        return ("xielu", self.act_up, self.act_down) if self.learned else self.spec.activation
 
     def first_product(self):
         return self.w_up, self.b_up, self._first_activation()
@@ -65,8 +65,6 @@ class DenseFeedForward(FeedForward):
     def until_last(self, xn, ctx, first=None):
         h = first if first is not None else ops.linear(xn, self.w_up, self.b_up, act=self._first_activation(),
                                                        out_dtype=ctx.act_dtype)
-        if self.learned:
-            ops.xielu(h, self.act_up, self.act_down)
         return h, self.w_down, self.b_down
 
     def forward(self, xn, ctx, add: Sequence[torch.Tensor], out: torch.Tensor) -> torch.Tensor:

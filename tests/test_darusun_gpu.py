@@ -494,6 +494,18 @@ def test_kernels_of_the_design_alone():
                 c, s = torch.cos(ang)[:, None], torch.sin(ang)[:, None]
                 turned = torch.stack([a * c - b * s, b * c + a * s], -1).reshape(T, H, tail)        # (the copied columns are not gated)
                 assert (got[..., N:] - turned).abs().max() <= tol * max(1.0, turned.abs().max())
+    # the activation with two numbers: in the epilogue of every product kernel (few rows, many rows, 32-bit) and alone
+    def xielu(z, up, down):
+        return torch.where(z > 0, up * z * z + 0.5 * z, down * (torch.expm1(torch.clamp(z, max=0.0)) - z) + 0.5 * z)
+    for rows in (5, 200):
+        a, w = torch.randn(rows, 64, generator=g), torch.randn(48, 64, generator=g) * 0.2
+        for dtype, tol in ((torch.float32, 1e-5), (torch.bfloat16, 3e-2)):
+            ad, wd = a.to(dev, dtype), w.to(dev, dtype)
+            want = xielu(ad.float().cpu() @ wd.float().cpu().T, 0.7, 1.3)
+            got = ops.linear(ad, wd, None, act=("xielu", 0.7, 1.3), out_dtype=torch.float32).cpu()
+            assert (got - want).abs().max() <= tol * max(1.0, want.abs().max()), (rows, dtype)
+            alone = ops.xielu((ad.float() @ wd.float().T).to(dtype), 0.7, 1.3).float().cpu()
+            assert (alone - want).abs().max() <= tol * max(1.0, want.abs().max())
     logits = torch.randn(50, 7, generator=g)
     bias = torch.randn(7, generator=g)
     ids, weights = ops.moe_route(logits.to(dev), 3, bias=bias.to(dev), softmax_chosen=True)
