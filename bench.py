@@ -402,7 +402,7 @@ def darusun_sizes(width, heads, ff):
             {"type": "latent_attention", "mixer": latent, "mlp": moe}, {"type": "attention", "mixer": attn, "mlp": dense}]
     second = json.loads(json.dumps(five))
     second[2]["mixer"]["kv_from"] = 6
-    return {"architecture": "Darusun", "vocab": 32000, "width": width, "norm": {"eps": 1e-6}, "residual_mult": 0.7,
+    return {"architecture": "Darusun", "vocab": 32000, "width": width, "norm": {"eps": 1e-6}, "residual_mult": 0.5,
             "initializer_range": 0.02, "layers": five + second}
 
 
