@@ -1703,9 +1703,13 @@ def moe_experts(x: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, w_gat
     Which kernels run depends on the step's size alone: up to MOE_ROWS_KERNEL_PER_EXPERT pairs an expert on
     average (bfloat16) a weight-streaming kernel, a warp an output column; more (bfloat16): every expert's rows on
     tiles of 128 of their own and each product one tcgen05 product with grouped weights; other types: tiles of 32
-    rows on the CUDA cores, every sum over k in ascending order."""
+    rows on the CUDA cores, every sum over k in ascending order.  ``add`` may be a callable that returns the tensor:
+    it is called right before the last kernel, the one that adds it (a branch on a second stream joins there)."""
     _need(x, "x")
     T, K = x.shape
+    late_add = add if callable(add) else None
+    if late_add is not None:
+        add = None
     _need(ids, "ids", torch.int32)
     top = ids.shape[1]
     _need(weights, "weights", torch.float32, (T, top))
@@ -1740,6 +1744,9 @@ def moe_experts(x: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, w_gat
         gu = gemm_tcgen05_grouped(xs, w_gate_up, tile_expert, torch.bfloat16)
         h = gated_act(gu, "silu")
         y = gemm_tcgen05_grouped(h, w_down, tile_expert, torch.float32)
+        if late_add is not None:
+            add = late_add()
+            _need(add, "add", torch.float32, (T, hidden))
         _check(_launch(lib.gl_moe_combine_placed, _ptr(y), _ptr(place), _ptr(weights), _ptr(add), _ptr(out), c_int(T),
                        c_int(hidden), c_int(top), _stream()), "moe_combine")
         return out
@@ -1761,6 +1768,9 @@ def moe_experts(x: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, w_gat
                     tile_start.data_ptr(), tile_rows.data_ptr(), n_tiles.data_ptr(), weights.data_ptr(), A, hidden, F, top,
                     max_tiles, E)
     _check(_launch(lib.gl_moe_down if USE_MOE_TC else lib.gl_moe_down_simt, byref(d), xd, wd, _stream()), "moe_down")
+    if late_add is not None:
+        add = late_add()
+        _need(add, "add", torch.float32, (T, hidden))
     _check(_launch(lib.gl_moe_combine, _ptr(y), _ptr(add), _ptr(out), c_int(T), c_int(hidden), c_int(top), _stream()),
            "moe_combine")
     return out

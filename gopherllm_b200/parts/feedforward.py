@@ -238,7 +238,9 @@ class MixtureOfExperts(FeedForward):
         """(experts int32 [T, top], weights float32 [T, top]) of the step's tokens."""
         if self.router == "table":
             return ops.moe_route_table(ctx.tokens, self.table, self.E)
-        if xn.dtype == torch.bfloat16 and self.w_router_16 is not None and xn.shape[1] % 8 == 0:
+        # (few tokens: product and choice as one kernel, a block a token, rather than two short kernels in a row)
+        if (xn.dtype == torch.bfloat16 and self.w_router_16 is not None and xn.shape[1] % 8 == 0
+                and not (xn.shape[0] <= 64 and self.weights_by == "softmax_chosen")):
             logits = ops.linear(xn, self.w_router_16, None, out_dtype=torch.float32)
             return ops.moe_route(logits, self.top, self.groups, self.keep, self.scale, self.b_router,
                                  self.weights_by == "softmax_chosen")
@@ -248,6 +250,29 @@ class MixtureOfExperts(FeedForward):
     def forward(self, xn, ctx, add: Sequence[torch.Tensor], out=None) -> torch.Tensor:
         if len(add) > (2 if self.shared else 1):
             raise ValueError("more tensors to add than this feed-forward's kernels take")
+        side = getattr(ctx, "side_stream", None)
+        if self.shared and side is not None and len(add) <= 1 and torch.cuda.current_stream() != side:
+            # few tokens: every kernel is short, and the shared expert's three do not depend on the router.  They run on
+            # a second stream beside the routing and the chosen experts' products and join in the kernel that sums a
+            # token's experts (the same sums in another order: (shared + what is to be added) + experts).
+            main = torch.cuda.current_stream()
+            ys = ops.empty((xn.shape[0], self.spec.hidden), torch.float32, xn.device)
+            fork, join = torch.cuda.Event(), torch.cuda.Event()
+            fork.record(main)
+            side.wait_event(fork)
+            with torch.cuda.stream(side):
+                gu = ops.linear(xn, self.ws_gu, None, out_dtype=ctx.act_dtype)
+                hs = (ops.gated_act(gu, "silu", inner=self.shared, row_gate=2 * self.shared) if self.shared_gate
+                      else ops.gated_act(gu, "silu"))
+                ops.linear(hs, self.ws_down, None, add0=add[0] if len(add) > 0 else None, out_dtype=torch.float32, out=ys)
+                join.record(side)
+
+            def shared():
+                main.wait_event(join)
+                return ys
+
+            ids, weights = self.route(xn, ctx)
+            return ops.moe_experts(xn, ids, weights, self.w_gu, self.w_down, add=shared, out=out)
         ids, weights = self.route(xn, ctx)
         out = ops.moe_experts(xn, ids, weights, self.w_gu, self.w_down, add=add[0] if len(add) > 0 else None, out=out)
         if self.shared:
