@@ -238,9 +238,7 @@ class MixtureOfExperts(FeedForward):
         """(experts int32 [T, top], weights float32 [T, top]) of the step's tokens."""
         if self.router == "table":
             return ops.moe_route_table(ctx.tokens, self.table, self.E)
-        # (few tokens: product and choice as one kernel, a block a token, rather than two short kernels in a row)
-        if (xn.dtype == torch.bfloat16 and self.w_router_16 is not None and xn.shape[1] % 8 == 0
-                and not (xn.shape[0] <= 64 and self.weights_by == "softmax_chosen")):
+        if xn.dtype == torch.bfloat16 and self.w_router_16 is not None and xn.shape[1] % 8 == 0:
             logits = ops.linear(xn, self.w_router_16, None, out_dtype=torch.float32)
             return ops.moe_route(logits, self.top, self.groups, self.keep, self.scale, self.b_router,
                                  self.weights_by == "softmax_chosen")
